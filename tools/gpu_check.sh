@@ -9,7 +9,7 @@ timeout 600 python bench.py > gpurun_out/r02_bench_n1.json 2> gpurun_out/r02_ben
 timeout 400 python bench.py --impl reference --steps 3 --warmup 1 > gpurun_out/r02_bench_reference_arm.json 2> gpurun_out/r02_bench_ref.err; head -c 500 gpurun_out/r02_bench_reference_arm.json; echo
 if [ "${NCU:-1}" = "1" ]; then
   timeout 500 ncu --metrics gpu__time_duration.sum --clock-control none --kernel-name-base demangled -k regex:'k_' -c 400 --csv --log-file gpurun_out/r02_launches_default_bench_raw.csv python bench.py --steps 4 --warmup 3 --no-cpu --no-single > gpurun_out/r02_ncu_launch.log 2>&1; tail -2 gpurun_out/r02_ncu_launch.log | cut -c1-300
-  timeout 500 ncu --set full --clock-control none --import-source on --kernel-name-base demangled -k regex:'k_shard_step' -s 4 -c 1 -o gpurun_out/r02_prof_step python bench.py --steps 4 --warmup 3 --no-cpu --no-single > gpurun_out/r02_ncu_step.log 2>&1; tail -2 gpurun_out/r02_ncu_step.log | cut -c1-300
+  timeout 500 ncu --set full --clock-control none --kernel-name-base demangled -k regex:'k_shard_step' -s 4 -c 1 -o gpurun_out/r02_prof_step python bench.py --steps 4 --warmup 3 --no-cpu --no-single > gpurun_out/r02_ncu_step.log 2>&1; tail -2 gpurun_out/r02_ncu_step.log | cut -c1-300
   ncu -i gpurun_out/r02_prof_step.ncu-rep --page raw --csv > gpurun_out/r02_ncu_step_raw.csv 2>/dev/null; wc -l gpurun_out/r02_ncu_step_raw.csv
 fi
 # driver settings (what the round-end bench runs) and the MoE config on one GPU
