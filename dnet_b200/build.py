@@ -8,7 +8,12 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 SRC = ROOT / "csrc" / "dn_api.cu"
-DEPS = [*sorted((ROOT / "csrc").glob("*.cu*")), ROOT.parent / "include" / "dnet_b200.h"]
+# the batched sequence-mixer step is a library of its own: a process that serves such a model compiles and loads
+# only this one
+SEQ_SRC = ROOT / "csrc" / "dn_seq.cu"
+SEQ_DEPS = [*sorted((ROOT / "csrc").glob("dn_seq*.cu*")), ROOT.parent / "include" / "dnet_b200_seq.h"]
+SEQ_OUT = ROOT / "lib" / "libdnet_b200_seq.so"
+DEPS = [d for d in [*sorted((ROOT / "csrc").glob("*.cu*")), ROOT.parent / "include" / "dnet_b200.h"] if d not in SEQ_DEPS]
 OUT = ROOT / "lib" / "libdnet_b200.so"
 
 NVCC_FLAGS = [
@@ -18,11 +23,11 @@ NVCC_FLAGS = [
 ]
 
 
-def needs_build() -> bool:
-    if not OUT.exists():
+def needs_build(out: Path = OUT, deps=None) -> bool:
+    if not out.exists():
         return True
-    t = OUT.stat().st_mtime
-    return any(d.stat().st_mtime > t for d in DEPS)
+    t = out.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in (DEPS if deps is None else deps))
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
@@ -39,5 +44,26 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return OUT
 
 
+def build_seq(force: bool = False, verbose: bool = False) -> Path:
+    """libdnet_b200_seq.so; concurrent first calls build into private files and rename."""
+    if not force and not needs_build(SEQ_OUT, SEQ_DEPS):
+        return SEQ_OUT
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    SEQ_OUT.parent.mkdir(parents=True, exist_ok=True)
+    tmp = SEQ_OUT.with_name(f".{SEQ_OUT.name}.{os.getpid()}")
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp), str(SEQ_SRC)]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+        print(" ".join(cmd), file=sys.stderr)
+    try:
+        subprocess.run(cmd, check=True, stdout=sys.stderr)
+        os.replace(tmp, SEQ_OUT)
+    finally:
+        if tmp.exists():
+            tmp.unlink()
+    return SEQ_OUT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_seq(force="--force" in sys.argv, verbose="-v" in sys.argv))

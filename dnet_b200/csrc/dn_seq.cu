@@ -1,0 +1,415 @@
+// dn_seq.cu -- C ABI of libdnet_b200_seq.so (include/dnet_b200_seq.h): host bookkeeping of the batched step --
+// bound weight pointers, the page pool and the state slots, the staging of a step's batch description, and the
+// launch sequence of a layer.  All arithmetic is in dn_seq_kernels.cuh.
+#include "dn_seq_kernels.cuh"
+#include "../../include/dnet_b200_seq.h"
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+using namespace dnseq;
+
+#define DN_OK 0
+#define DN_EINVAL (-22)
+#define DN_ENOMEM (-12)
+#define DN_ENOENT (-2)
+#define DN_ECUDA (-5)
+#define DN_ENOSPC (-28)
+
+static thread_local char g_err[512] = "";
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+#define CK(...)                                                                                                 \
+  do {                                                                                                          \
+    cudaError_t e_ = (__VA_ARGS__);                                                                             \
+    if (e_ != cudaSuccess)                                                                                      \
+      return fail(DN_ECUDA, "%s failed: %s (%s:%d)", #__VA_ARGS__, cudaGetErrorString(e_), __FILE__, __LINE__); \
+  } while (0)
+
+static std::atomic<long long> g_launches{0};
+static int g_device = -1;
+static int g_sms = 0;
+static size_t g_max_smem = 0;
+
+struct SeqLayer {
+  dn_seq_layer_cfg c;
+  const void* w[DN_SQ_COUNT];
+  int Cq, Ck, Cv, Co;           // projection widths: q, k, v and the mixer's output before W_o
+  int kv_index;                 // attention: which page pool (own or the one it borrows); -1 for delta
+  size_t conv_off, delta_off;   // element offsets into a slot's carried conv inputs / fp32 delta state
+  float* inv_freq;              // [rot/2] device
+};
+
+struct dn_seq_model {
+  dn_seq_cfg cfg;
+  std::vector<SeqLayer> L;
+  const void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
+  size_t esz = 2;
+  int S1 = 1, MB = 0, max_pages = 0;
+  // scratch
+  float *xs = nullptr, *y = nullptr, *pa = nullptr, *pb = nullptr, *qn = nullptr, *kn = nullptr, *vv = nullptr, *od = nullptr,
+        *beta = nullptr, *decay = nullptr;
+  void *h = nullptr, *uq = nullptr, *uk = nullptr, *uv = nullptr, *qb = nullptr, *mo = nullptr, *gt = nullptr, *act = nullptr;
+  // state
+  std::vector<void*> kpool, vpool;
+  void* conv_state = nullptr;
+  size_t conv_stride = 0;       // elements per slot
+  float* delta_state = nullptr;
+  size_t delta_stride = 0;
+  std::vector<int> free_pages, free_slots;
+  std::vector<std::vector<int>> pages;   // per slot
+  std::vector<int> length;               // per slot, -1: closed
+  // staging
+  int32_t *stage_h = nullptr, *stage_d = nullptr, *bt_h = nullptr, *bt_d = nullptr;
+  size_t stage_ints = 0;
+  cudaEvent_t staged = nullptr;
+};
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  g_launches++;
+  kern<<<grid, block, smem, s>>>(static_cast<KArgs>(args)...);
+  return cudaGetLastError();
+}
+
+extern "C" const char* dn_seq_last_error(void) { return g_err; }
+extern "C" int64_t dn_seq_launch_count(void) { return (int64_t)g_launches.load(); }
+
+extern "C" int dn_seq_init(int device) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return fail(DN_ECUDA, "no CUDA device visible (%s): libdnet_b200_seq has no CPU fallback", cudaGetErrorString(e));
+  if (device < 0 || device >= n) return fail(DN_EINVAL, "device %d out of range [0,%d)", device, n);
+  CK(cudaSetDevice(device));
+  cudaDeviceProp p;
+  CK(cudaGetDeviceProperties(&p, device));
+  if (p.major != 10) return fail(DN_EINVAL, "device %d is sm_%d%d; this library is built for sm_100a only", device, p.major, p.minor);
+  g_sms = p.multiProcessorCount;
+  g_max_smem = p.sharedMemPerBlockOptin;
+  g_device = device;
+  return DN_OK;
+}
+
+template <class P>
+static int dalloc(P** p, size_t bytes) {
+  void* q = nullptr;
+  if (cudaMalloc(&q, bytes ? bytes : 16) != cudaSuccess) return fail(DN_ENOMEM, "cudaMalloc of %zu bytes failed", bytes);
+  *p = (P*)q;
+  return DN_OK;
+}
+
+extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
+  if (!m) return DN_OK;
+  cudaDeviceSynchronize();
+  void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
+                  m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d};
+  for (void* p : ptrs) if (p) cudaFree(p);
+  for (void* p : m->kpool) if (p) cudaFree(p);
+  for (void* p : m->vpool) if (p) cudaFree(p);
+  for (auto& l : m->L) if (l.inv_freq) cudaFree(l.inv_freq);
+  if (m->stage_h) cudaFreeHost(m->stage_h);
+  if (m->bt_h) cudaFreeHost(m->bt_h);
+  if (m->staged) cudaEventDestroy(m->staged);
+  delete m;
+  return DN_OK;
+}
+
+extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg* layers, dn_seq_model** out) {
+  if (!cfg || !layers || !out) return fail(DN_EINVAL, "null argument");
+  if (g_device < 0) return fail(DN_EINVAL, "dn_seq_init() has not been called");
+  if (cfg->width <= 0 || cfg->vocab <= 0 || cfg->n_layers <= 0) return fail(DN_EINVAL, "width / vocab / n_layers must be positive");
+  if (cfg->streams < 0 || cfg->streams > MAX_STREAMS) return fail(DN_EINVAL, "streams %d unsupported (0..%d)", cfg->streams, MAX_STREAMS);
+  if (cfg->dtype != DN_SEQ_BF16 && cfg->dtype != DN_SEQ_F32) return fail(DN_EINVAL, "dtype %d unsupported", cfg->dtype);
+  if (cfg->pool_pages <= 0 || cfg->max_seqs <= 0 || cfg->max_batch_tokens <= 0) return fail(DN_EINVAL, "pool / slots / batch must be positive");
+  dn_seq_model* m = new (std::nothrow) dn_seq_model();
+  if (!m) return fail(DN_ENOMEM, "out of host memory");
+  m->cfg = *cfg;
+  m->esz = cfg->dtype == DN_SEQ_F32 ? 4 : 2;
+  m->S1 = cfg->streams > 0 ? cfg->streams : 1;
+  m->MB = cfg->max_batch_tokens;
+  m->max_pages = cfg->pool_pages;
+  m->L.resize(cfg->n_layers);
+  int mq = 1, mk = 1, mv = 1, mo = 1, mh = 1, mff = 1, mdq = 1;
+  size_t coff = 0, doff = 0;
+  int rc = DN_OK;
+  for (int i = 0; i < cfg->n_layers && rc == DN_OK; i++) {
+    SeqLayer& l = m->L[i];
+    l.c = layers[i];
+    memset(l.w, 0, sizeof(l.w));
+    l.inv_freq = nullptr;
+    l.kv_index = -1;
+    const dn_seq_layer_cfg& c = l.c;
+    if (c.heads <= 0 || c.kv_heads <= 0 || c.heads % c.kv_heads || c.dim <= 0 || c.vdim <= 0) {
+      rc = fail(DN_EINVAL, "layer %d: heads %d / kv_heads %d / dim %d / vdim %d unsupported", i, c.heads, c.kv_heads, c.dim, c.vdim);
+      break;
+    }
+    if (c.conv < 0 || c.conv > 9) { rc = fail(DN_EINVAL, "layer %d: conv taps %d unsupported (0..9)", i, c.conv); break; }
+    if (c.mixer == DN_MIX_ATTENTION) {
+      if (c.vdim > 256) { rc = fail(DN_EINVAL, "layer %d: vdim %d > 256", i, c.vdim); break; }
+      if (c.rot_dims < 0 || c.rot_dims > c.dim || (c.rot_dims & 1)) { rc = fail(DN_EINVAL, "layer %d: rot dims %d unsupported", i, c.rot_dims); break; }
+      l.Cq = c.heads * c.dim;
+      l.Co = c.heads * c.vdim;
+      if (c.kv_from >= 0) {
+        if (c.kv_from >= i || m->L[c.kv_from].c.mixer != DN_MIX_ATTENTION || m->L[c.kv_from].c.kv_from >= 0 ||
+            m->L[c.kv_from].c.kv_heads != c.kv_heads || m->L[c.kv_from].c.dim != c.dim || m->L[c.kv_from].c.vdim != c.vdim) {
+          rc = fail(DN_EINVAL, "layer %d: kv_from %d must name an earlier attention layer with its own keys and the same head sizes", i, c.kv_from);
+          break;
+        }
+        l.kv_index = m->L[c.kv_from].kv_index;
+        l.Ck = l.Cv = 0;
+      } else {
+        l.Ck = c.kv_heads * c.dim;
+        l.Cv = c.kv_heads * c.vdim;
+        l.kv_index = (int)m->kpool.size();
+        m->kpool.push_back(nullptr);
+        m->vpool.push_back(nullptr);
+        if ((rc = dalloc(&m->kpool.back(), (size_t)cfg->pool_pages * PAGE * l.Ck * m->esz)) != DN_OK) break;
+        if ((rc = dalloc(&m->vpool.back(), (size_t)cfg->pool_pages * PAGE * l.Cv * m->esz)) != DN_OK) break;
+      }
+      if (c.rot_dims > 0) {
+        std::vector<float> f(c.rot_dims / 2);
+        for (int j = 0; j < c.rot_dims / 2; j++) f[j] = (float)std::pow((double)c.rot_base, -2.0 * j / (double)c.rot_dims);
+        if ((rc = dalloc(&l.inv_freq, f.size() * 4)) != DN_OK) break;
+        if (cudaMemcpy(l.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) { rc = fail(DN_ECUDA, "inv_freq upload failed"); break; }
+      }
+    } else if (c.mixer == DN_MIX_DELTA) {
+      if (c.dim > 1024) { rc = fail(DN_EINVAL, "layer %d: delta dim %d > 1024", i, c.dim); break; }
+      l.Cq = l.Ck = c.kv_heads * c.dim;
+      l.Cv = l.Co = c.heads * c.vdim;
+      l.delta_off = doff;
+      doff += (size_t)c.heads * c.dim * c.vdim;
+      mdq = std::max(mdq, l.Cq);
+    } else {
+      rc = fail(DN_EINVAL, "layer %d: mixer %d unknown", i, c.mixer);
+      break;
+    }
+    l.conv_off = coff;
+    if (c.conv > 1) coff += (size_t)(c.conv - 1) * (l.Cq + l.Ck + l.Cv);
+    mq = std::max(mq, l.Cq); mk = std::max(mk, l.Ck); mv = std::max(mv, l.Cv); mo = std::max(mo, l.Co);
+    mh = std::max(mh, c.heads); mff = std::max(mff, c.ff);
+  }
+  const size_t MB = m->MB, W = cfg->width, e = m->esz;
+  m->conv_stride = coff;
+  m->delta_stride = doff;
+#define DA(p, bytes) if (rc == DN_OK) rc = dalloc(&p, (bytes))
+  DA(m->xs, (size_t)m->S1 * MB * W * 4); DA(m->y, MB * W * 4); DA(m->pa, MB * mh * 4); DA(m->pb, MB * mh * 4);
+  DA(m->qn, MB * mdq * 4); DA(m->kn, MB * mdq * 4); DA(m->vv, MB * mo * 4); DA(m->od, MB * mo * 4);
+  DA(m->beta, MB * mh * 4); DA(m->decay, MB * mh * 4);
+  DA(m->h, MB * W * e); DA(m->uq, MB * mq * e); DA(m->uk, MB * mk * e); DA(m->uv, MB * mv * e); DA(m->qb, MB * mq * e);
+  DA(m->mo, MB * mo * e); DA(m->gt, MB * mo * e); DA(m->act, MB * mff * e);
+  DA(m->conv_state, (size_t)cfg->max_seqs * coff * e); DA(m->delta_state, (size_t)cfg->max_seqs * doff * 4);
+  m->stage_ints = 4 * MB + 3 * (size_t)(cfg->max_seqs + 1) + MB;
+  DA(m->stage_d, m->stage_ints * 4); DA(m->bt_d, (size_t)cfg->max_seqs * m->max_pages * 4);
+#undef DA
+  if (rc == DN_OK && cudaHostAlloc((void**)&m->stage_h, m->stage_ints * 4, cudaHostAllocPortable) != cudaSuccess) rc = fail(DN_ENOMEM, "pinned staging failed");
+  if (rc == DN_OK && cudaHostAlloc((void**)&m->bt_h, (size_t)cfg->max_seqs * m->max_pages * 4, cudaHostAllocPortable) != cudaSuccess) rc = fail(DN_ENOMEM, "pinned block table failed");
+  if (rc == DN_OK && cudaEventCreateWithFlags(&m->staged, cudaEventDisableTiming) != cudaSuccess) rc = fail(DN_ECUDA, "event creation failed");
+  if (rc != DN_OK) { dn_seq_model_destroy(m); return rc; }
+  for (int p = cfg->pool_pages - 1; p >= 0; p--) m->free_pages.push_back(p);
+  for (int s = cfg->max_seqs - 1; s >= 0; s--) m->free_slots.push_back(s);
+  m->pages.resize(cfg->max_seqs);
+  m->length.assign(cfg->max_seqs, -1);
+  *out = m;
+  return DN_OK;
+}
+
+extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p) {
+  if (!m) return fail(DN_EINVAL, "null model");
+  if (layer < 0) {
+    if (which == DN_SQ_EMBED) m->embed = p;
+    else if (which == DN_SQ_FINAL_NORM) m->final_norm = p;
+    else if (which == DN_SQ_HEAD) m->head = p;
+    else return fail(DN_EINVAL, "tensor %d is not a model tensor", which);
+    return DN_OK;
+  }
+  if (layer >= (int)m->L.size() || which < 0 || which >= DN_SQ_COUNT) return fail(DN_EINVAL, "layer %d / tensor %d out of range", layer, which);
+  m->L[layer].w[which] = p;
+  return DN_OK;
+}
+
+extern "C" int dn_seq_open(dn_seq_model* m, dn_seq_stream s, int* slot_out) {
+  if (!m || !slot_out) return fail(DN_EINVAL, "null argument");
+  if (m->free_slots.empty()) return fail(DN_ENOSPC, "all %d state slots are in use", m->cfg.max_seqs);
+  const int slot = m->free_slots.back();
+  // the slot's recurrent state and carried conv inputs start at zero, behind whatever still reads the slot on s
+  if (m->conv_stride) CK(cudaMemsetAsync((char*)m->conv_state + (size_t)slot * m->conv_stride * m->esz, 0, m->conv_stride * m->esz, (cudaStream_t)s));
+  if (m->delta_stride) CK(cudaMemsetAsync(m->delta_state + (size_t)slot * m->delta_stride, 0, m->delta_stride * 4, (cudaStream_t)s));
+  m->free_slots.pop_back();
+  m->length[slot] = 0;
+  m->pages[slot].clear();
+  *slot_out = slot;
+  return DN_OK;
+}
+
+extern "C" int dn_seq_close(dn_seq_model* m, int slot) {
+  if (!m || slot < 0 || slot >= m->cfg.max_seqs || m->length[slot] < 0) return fail(DN_EINVAL, "slot %d is not open", slot);
+  for (auto it = m->pages[slot].rbegin(); it != m->pages[slot].rend(); ++it) m->free_pages.push_back(*it);
+  m->pages[slot].clear();
+  m->length[slot] = -1;
+  m->free_slots.push_back(slot);
+  return DN_OK;
+}
+
+extern "C" int dn_seq_length(dn_seq_model* m, int slot) {
+  if (!m || slot < 0 || slot >= m->cfg.max_seqs) return DN_EINVAL;
+  return m->length[slot];
+}
+extern "C" int dn_seq_free_pages(dn_seq_model* m) { return m ? (int)m->free_pages.size() : DN_EINVAL; }
+extern "C" int dn_seq_free_slots(dn_seq_model* m) { return m ? (int)m->free_slots.size() : DN_EINVAL; }
+
+// ---------------------------------------------------------------------------------------------------------------
+template <class T>
+static cudaError_t linear(cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32, int act) {
+  dim3 grid((O + 63) / 64, (N + 63) / 64);
+  if (out32) return launch(k_linear<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
+  return launch(k_linear<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
+}
+
+template <class T>
+static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* want_dev, float* logits, float* trace, cudaStream_t s) {
+  const dn_seq_cfg& c = m->cfg;
+  const int N = b.N, W = c.width, S = c.streams, S1 = m->S1;
+  const size_t nsm = ((size_t)W + 40) * 4;
+  const int ew = (int)(((size_t)N * W + 255) / 256);
+  CK(launch(k_embed<T>, dim3(N), dim3(128), 0, s, (const T*)m->embed, b, c.embed_scale, W, S1, m->xs));
+  for (int li = 0; li < c.n_layers; li++) {
+    SeqLayer& l = m->L[li];
+    const dn_seq_layer_cfg& lc = l.c;
+    auto w = [&](int i) { return (const T*)l.w[i]; };
+    // ---- mixer sublayer
+    CK(launch(k_read_norm<T>, dim3(N), dim3(128), nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
+    T* cst = (T*)m->conv_state + l.conv_off;
+    CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0));
+    if (l.Ck) CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0));
+    if (l.Cv) CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0));
+    if (lc.mixer == DN_MIX_ATTENTION) {
+      AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, c.eps, l.inv_freq};
+      const size_t sm = ((size_t)l.Cq + l.Ck + 40) * 4;
+      CK(launch(k_attn_prep<T>, dim3(N), dim3(256), sm, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_Q_CONV),
+                w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), w(DN_SQ_Q_NORM), w(DN_SQ_K_NORM), (const T*)cst, m->conv_stride, (T*)m->qb,
+                (T*)m->kpool[l.kv_index], (T*)m->vpool[l.kv_index]));
+      CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(32), (size_t)lc.dim * 4, s, b, (const T*)m->qb, (const T*)m->kpool[l.kv_index],
+                (const T*)m->vpool[l.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, (T*)m->mo));
+    } else {
+      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0));
+      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_B], nullptr, m->pb, N, lc.heads, W, true, 0));
+      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0));
+      DeltaPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv};
+      CK(launch(k_delta_prep<T>, dim3(N), dim3(256), (size_t)2 * l.Cq * 4, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
+                w(DN_SQ_Q_CONV), w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), (const float*)m->pa, (const float*)m->pb, w(DN_SQ_A_LOG),
+                w(DN_SQ_DT_BIAS), (const T*)cst, m->conv_stride, m->qn, m->kn, m->vv, m->beta, m->decay));
+      int R = lc.dim >= 32 ? 16 : 8, P = 1;
+      while (P * R < lc.dim) P <<= 1;
+      if (P > 32) { R = 32; P = 32; }
+      dim3 grid(b.E * lc.heads, (lc.vdim + 31) / 32);
+      float* st = m->delta_state + l.delta_off;
+#define DR(Rv) CK(launch(k_delta_rule<Rv>, grid, dim3(32 * P), 0, s, b, lc.heads, lc.kv_heads, lc.dim, lc.vdim, P, (const float*)m->qn, \
+                         (const float*)m->kn, (const float*)m->vv, (const float*)m->beta, (const float*)m->decay, st, m->delta_stride, m->od))
+      if (R == 8) DR(8); else if (R == 16) DR(16); else DR(32);
+#undef DR
+      CK(launch(k_delta_out<T>, dim3(N, lc.heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_OUT_NORM), lc.heads, lc.vdim,
+                c.eps, (T*)m->mo));
+    }
+    if (lc.conv > 1) {
+      const int ld = l.Cq + l.Ck + l.Cv;
+      CK(launch(k_conv_carry<T>, dim3((l.Cq + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uq, l.Cq, lc.conv, b, cst, m->conv_stride, ld, 0));
+      if (l.Ck) CK(launch(k_conv_carry<T>, dim3((l.Ck + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uk, l.Ck, lc.conv, b, cst, m->conv_stride, ld, l.Cq));
+      if (l.Cv) CK(launch(k_conv_carry<T>, dim3((l.Cv + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uv, l.Cv, lc.conv, b, cst, m->conv_stride, ld, l.Cq + l.Ck));
+    }
+    CK(linear<T>(s, (const T*)m->mo, l.w[DN_SQ_O], nullptr, m->y, N, W, l.Co, true, 0));
+    CK(launch(k_write_back<T>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, w(DN_SQ_HC1_MIX), w(DN_SQ_HC1_OUT), (const float*)m->y));
+    // ---- feed-forward sublayer
+    if (lc.ff > 0) {
+      CK(launch(k_read_norm<T>, dim3(N), dim3(128), nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
+      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, 1));
+      CK(linear<T>(s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0));
+      CK(launch(k_write_back<T>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, w(DN_SQ_HC2_MIX), w(DN_SQ_HC2_OUT), (const float*)m->y));
+    }
+    if (trace) CK(launch(k_stream_sum, dim3(ew), dim3(256), 0, s, (const float*)m->xs, N, W, S1, trace + (size_t)li * N * W));
+  }
+  if (n_want > 0) {
+    CK(launch(k_read_norm<T>, dim3(n_want), dim3(128), nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, 1, 1, c.eps, want_dev, (T*)m->h));
+    CK(linear<T>(s, (const T*)m->h, m->head, nullptr, logits, n_want, c.vocab, W, true, 0));
+  }
+  return DN_OK;
+}
+
+extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const int32_t* counts, const int32_t* tokens, int n_want,
+                           const int32_t* want, float* logits, float* trace, dn_seq_stream sp) {
+  if (!m || E <= 0 || !slots || !counts || !tokens || (n_want > 0 && (!want || !logits))) return fail(DN_EINVAL, "bad argument");
+  if (E > m->cfg.max_seqs) return fail(DN_EINVAL, "%d entries > %d state slots", E, m->cfg.max_seqs);
+  cudaStream_t s = (cudaStream_t)sp;
+  int N = 0;
+  size_t need = 0;
+  for (int e = 0; e < E; e++) {
+    const int sl = slots[e];
+    if (sl < 0 || sl >= m->cfg.max_seqs || m->length[sl] < 0) return fail(DN_EINVAL, "entry %d: slot %d is not open", e, sl);
+    for (int f = 0; f < e; f++) if (slots[f] == sl) return fail(DN_EINVAL, "slot %d appears twice in one step", sl);
+    if (counts[e] <= 0) return fail(DN_EINVAL, "entry %d brings no tokens", e);
+    N += counts[e];
+    const size_t pages = ((size_t)m->length[sl] + counts[e] + PAGE - 1) / PAGE;
+    if (pages > (size_t)m->max_pages) return fail(DN_ENOSPC, "sequence too long for the block table");
+    if (pages > m->pages[sl].size()) need += pages - m->pages[sl].size();
+  }
+  if (N > m->MB) return fail(DN_EINVAL, "%d tokens > max_batch_tokens %d", N, m->MB);
+  if (n_want > N) return fail(DN_EINVAL, "more wanted rows than tokens");
+  for (int i = 0; i < N; i++) if (tokens[i] < 0 || tokens[i] >= m->cfg.vocab) return fail(DN_EINVAL, "token id %d out of range", tokens[i]);
+  if (need > m->free_pages.size()) return fail(DN_ENOSPC, "cache pool exhausted: %zu pages needed, %zu free", need, m->free_pages.size());
+  for (int i = 0; i < n_want; i++) if (want[i] < 0 || want[i] >= N) return fail(DN_EINVAL, "wanted row %d out of range", want[i]);
+  if (!m->embed || !m->final_norm || !m->head) return fail(DN_ENOENT, "embedding / final norm / head are not bound");
+  for (int i = 0; i < m->cfg.n_layers; i++) {
+    const SeqLayer& l = m->L[i];
+    auto has = [&](int k) { return l.w[k] != nullptr; };
+    bool ok = has(DN_SQ_NORM1) && has(DN_SQ_Q) && has(DN_SQ_O) && (l.c.ff == 0 || (has(DN_SQ_NORM2) && has(DN_SQ_GATE) && has(DN_SQ_UP) && has(DN_SQ_DOWN)));
+    if (l.Ck) ok = ok && has(DN_SQ_K) && has(DN_SQ_V);
+    if (l.c.conv > 0) ok = ok && has(DN_SQ_Q_CONV) && (!l.Ck || (has(DN_SQ_K_CONV) && has(DN_SQ_V_CONV)));
+    if (l.c.mixer == DN_MIX_ATTENTION) ok = ok && has(DN_SQ_Q_NORM) && (!l.Ck || has(DN_SQ_K_NORM));
+    else ok = ok && has(DN_SQ_A) && has(DN_SQ_B) && has(DN_SQ_G) && has(DN_SQ_A_LOG) && has(DN_SQ_DT_BIAS) && has(DN_SQ_OUT_NORM);
+    if (m->cfg.streams > 0) ok = ok && has(DN_SQ_HC1_IN) && has(DN_SQ_HC1_OUT) && has(DN_SQ_HC1_MIX) &&
+                                 (l.c.ff == 0 || (has(DN_SQ_HC2_IN) && has(DN_SQ_HC2_OUT) && has(DN_SQ_HC2_MIX)));
+    if (!ok) return fail(DN_ENOENT, "layer %d: not every tensor of the layer is bound", i);
+  }
+  // the previous step's staging copies must have read the pinned buffers before they are rewritten
+  CK(cudaEventSynchronize(m->staged));
+  int32_t* h = m->stage_h;
+  int32_t *tok = h, *slot = h + N, *pos = h + 2 * N, *first = h + 3 * N, *es = h + 4 * N, *esl = es + E + 1, *ep0 = esl + E, *wr = ep0 + E;
+  int n = 0;
+  for (int e = 0; e < E; e++) {
+    const int sl = slots[e];
+    const size_t pages = ((size_t)m->length[sl] + counts[e] + PAGE - 1) / PAGE;
+    const size_t had = m->pages[sl].size();
+    while (m->pages[sl].size() < pages) {
+      const int pg = m->free_pages.back();
+      m->free_pages.pop_back();
+      m->bt_h[(size_t)sl * m->max_pages + m->pages[sl].size()] = pg;
+      m->pages[sl].push_back(pg);
+    }
+    if (pages > had)
+      CK(cudaMemcpyAsync(m->bt_d + (size_t)sl * m->max_pages + had, m->bt_h + (size_t)sl * m->max_pages + had, (pages - had) * 4,
+                         cudaMemcpyHostToDevice, s));
+    es[e] = n; esl[e] = sl; ep0[e] = m->length[sl];
+    for (int i = 0; i < counts[e]; i++, n++) { tok[n] = tokens[n]; slot[n] = sl; pos[n] = m->length[sl] + i; first[n] = es[e]; }
+    m->length[sl] += counts[e];
+  }
+  es[E] = N;
+  for (int i = 0; i < n_want; i++) wr[i] = want[i];
+  const size_t ints = 4 * (size_t)N + 3 * (size_t)E + 1 + n_want;
+  CK(cudaMemcpyAsync(m->stage_d, h, ints * 4, cudaMemcpyHostToDevice, s));
+  CK(cudaEventRecord(m->staged, s));
+  int32_t* d = m->stage_d;
+  Batch b{d, d + N, d + 2 * N, d + 3 * N, d + 4 * N, d + 4 * N + E + 1, d + 4 * N + 2 * E + 1, m->bt_d, N, E, m->max_pages};
+  const int32_t* want_dev = d + 4 * N + 3 * E + 1;
+  if (m->cfg.dtype == DN_SEQ_F32) return step_T<float>(m, b, n_want, want_dev, logits, trace, s);
+  return step_T<bf16>(m, b, n_want, want_dev, logits, trace, s);
+}

@@ -1,0 +1,476 @@
+// dn_seq_kernels.cuh -- kernels of the batched sequence-mixer path (libdnet_b200_seq.so).
+//
+// A step is a ragged batch: N tokens of E entries (one entry = the next tokens of one live sequence, a portion of
+// a prompt or a single decoded token).  Entry e owns the rows [ent_start[e], ent_start[e+1]) of every [N, *]
+// buffer; its tokens sit at positions ent_pos0[e].. of the sequence in state slot ent_slot[e].  Everything a token
+// computes depends only on its own row, its sequence's cache pages and its slot's recurrent state, and every
+// reduction runs in an order that does not depend on N, E or the page / slot numbers.
+//
+// Mechanisms (each with its constants as arguments, none tied to one model family):
+//   * residual streams ("hyper-connections"): S fp32 copies of the residual, a learned read-out before a sublayer
+//     and a learned S x S mix + write-back after it; S = 0 is the plain residual sum
+//   * RMS norm with a one-plus or a plain weight, over a row or over a whole projection
+//   * short causal depthwise convolution over time with the last taps-1 inputs carried per sequence
+//   * rotary embedding, interleaved pairs, on the first `rot` dims of each head
+//   * paged softmax attention with a causal mask restricted to the query's own block of `chunk` positions
+//     (chunk = 0: plain causal), GQA, separate key and value widths, optional reuse of another layer's pages
+//   * gated delta rule: per head a [dk, dv] fp32 state with decay, delta-rule write and read-out
+// T is the storage type of weights and activations (bf16 or float); sums, norms, scores, positions, gates and
+// states are fp32 in both.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dnseq {
+
+typedef __nv_bfloat16 bf16;
+constexpr int PAGE = 64;
+constexpr int MAX_STREAMS = 8;
+
+template <class T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <class T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over the block in a fixed order (warp partials added by index); red: >= 33 floats of shared memory
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// the batch of one step, all device pointers
+struct Batch {
+  const int32_t* tok;        // [N]
+  const int32_t* slot;       // [N]   state slot of the token's sequence
+  const int32_t* pos;        // [N]   position in its sequence
+  const int32_t* first;      // [N]   row of the first token of the token's entry
+  const int32_t* ent_start;  // [E+1]
+  const int32_t* ent_slot;   // [E]
+  const int32_t* ent_pos0;   // [E]
+  const int32_t* bt;         // [slots][max_pages] page of each 64-token block
+  int N, E, max_pages;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// embedding -> residual streams
+template <class T>
+__global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W, int S1, float* __restrict__ xs) {
+  const int n = blockIdx.x;
+  const size_t row = (size_t)b.tok[n] * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = ldf(embed + row + c) * scale;
+    for (int s = 0; s < S1; s++) xs[((size_t)s * b.N + n) * W + c] = v;
+  }
+}
+
+// stream read-out (u = sum_s in[s] x_s, or x_0) + RMS norm with weight (1 + w) or w; rows[] optionally gathers
+template <class T>
+__global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, const T* __restrict__ hc_in, const T* __restrict__ nw,
+                            int one_plus, int sum_all, float eps, const int32_t* __restrict__ rows, T* __restrict__ h) {
+  extern __shared__ float sm[];
+  float* u = sm;            // [W]
+  float* red = sm + W;      // [33]
+  const int r = blockIdx.x, n = rows ? rows[r] : r;
+  float cin[MAX_STREAMS];
+  const int S1 = S > 0 ? S : 1;
+  for (int s = 0; s < S1; s++) cin[s] = (S > 0 && !sum_all) ? ldf(hc_in + s) : 1.f;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < S1; s++) a += cin[s] * xs[((size_t)s * N + n) * W + c];
+    u[c] = a;
+    ss += a * a;
+  }
+  ss = block_sum(ss, red);
+  const float rinv = 1.f / sqrtf(ss / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float g = ldf(nw + c) + (one_plus ? 1.f : 0.f);
+    stf(h + (size_t)r * W + c, u[c] * rinv * g);
+  }
+}
+
+// stream write-back: x_t <- sum_s mix[s][t] x_s + out[t] y   (S = 0: x <- x + y)
+template <class T>
+__global__ void k_write_back(float* __restrict__ xs, int N, int W, int S, const T* __restrict__ mix, const T* __restrict__ out,
+                             const float* __restrict__ y) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)N * W) return;
+  if (S <= 0) { xs[i] += y[i]; return; }
+  float x[MAX_STREAMS];
+  for (int s = 0; s < S; s++) x[s] = xs[(size_t)s * N * W + i];
+  const float yy = y[i];
+  for (int t = 0; t < S; t++) {
+    float a = 0.f;
+    for (int s = 0; s < S; s++) a += ldf(mix + s * S + t) * x[s];
+    xs[(size_t)t * N * W + i] = a + ldf(out + t) * yy;
+  }
+}
+
+// sum of the streams (inspection hook)
+__global__ void k_stream_sum(const float* __restrict__ xs, int N, int W, int S1, float* __restrict__ o) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)N * W) return;
+  float a = 0.f;
+  for (int s = 0; s < S1; s++) a += xs[(size_t)s * N * W + i];
+  o[i] = a;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Y[N, O] = X[N, K] W[O, K]^T, fp32 accumulation in ascending k; CUDA-core tiles (any N, O, K).
+// OUT32: write fp32 (residual-side outputs), else T.  act 0: none; 1: Y = gelu_tanh(X W^T) * (X W2^T).
+template <class T, bool OUT32>
+__global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
+                                                void* __restrict__ Y, int N, int O, int K, int act) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float Xs[BK][BM + 4], Ws[BK][BN + 4], Vs[BK][BN + 4];
+  const int n0 = blockIdx.y * BM, o0 = blockIdx.x * BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4], acc2[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = acc2[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int e = threadIdx.x; e < BM * BK; e += 256) {
+      const int r = e / BK, c = e % BK;
+      Xs[c][r] = (n0 + r < N && k0 + c < K) ? ldf(X + (size_t)(n0 + r) * K + k0 + c) : 0.f;
+      Ws[c][r] = (o0 + r < O && k0 + c < K) ? ldf(Wt + (size_t)(o0 + r) * K + k0 + c) : 0.f;
+      if (act) Vs[c][r] = (o0 + r < O && k0 + c < K) ? ldf(W2 + (size_t)(o0 + r) * K + k0 + c) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; k++) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = Xs[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) w[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+      if (act) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) w[j] = Vs[k][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc2[i][j] = fmaf(a[i], w[j], acc2[i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int n = n0 + ty * 4 + i;
+    if (n >= N) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int o = o0 + tx * 4 + j;
+      if (o >= O) continue;
+      float v = acc[i][j];
+      if (act) v = gelu_tanh_f(v) * acc2[i][j];
+      if (OUT32) ((float*)Y)[(size_t)n * O + o] = v;
+      else stf((T*)Y + (size_t)n * O + o, v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// short causal convolution: value of input channel c at `back` steps before row n of its entry
+template <class T>
+__device__ __forceinline__ float conv_in(const T* __restrict__ U, int ldu, int c, int n, int local, int back, const T* __restrict__ st,
+                                         int ldst, int taps) {
+  if (back <= local) return ldf(U + (size_t)(n - back) * ldu + c);
+  return ldf(st + (size_t)(taps - 1 - (back - local)) * ldst + c);   // carried inputs: st[taps-2] is the newest
+}
+template <class T>
+__device__ __forceinline__ float conv_at(const T* __restrict__ U, int ldu, const T* __restrict__ cw, int c, int n, int local,
+                                         const T* __restrict__ st, int ldst, int taps) {
+  if (taps <= 0) return ldf(U + (size_t)n * ldu + c);
+  float a = 0.f;
+  for (int j = 0; j < taps; j++) a += ldf(cw + (size_t)c * taps + j) * conv_in(U, ldu, c, n, local, taps - 1 - j, st, ldst, taps);
+  return a;
+}
+
+// after a step: the last taps-1 inputs of every entry become its slot's carried inputs
+template <class T>
+__global__ void k_conv_carry(const T* __restrict__ U, int C, int taps, Batch b, T* __restrict__ state, size_t slot_stride, int ldst,
+                             int coff) {
+  const int e = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int s0 = b.ent_start[e], len = b.ent_start[e + 1] - s0;
+  T* st = state + (size_t)b.ent_slot[e] * slot_stride + coff;
+  T keep[8];
+  const int m = taps - 1;
+  for (int j = 0; j < m; j++) {
+    const int idx = len - m + j;   // local index of the input that lands in st[j]
+    keep[j] = idx >= 0 ? U[(size_t)(s0 + idx) * C + c] : st[(size_t)(m + idx) * ldst + c];
+  }
+  for (int j = 0; j < m; j++) st[(size_t)j * ldst + c] = keep[j];
+}
+
+struct AttnPrep {
+  int H, G, dk, dv, taps, rot;       // heads, kv heads, key dim, value dim, conv taps (0: none), rotated dims
+  int own_kv;                        // 0: keys / values come from another layer's pages
+  float eps;
+  const float* inv_freq;             // [rot/2]
+};
+
+// attention mixer, between the projections and the scores: conv -> RMS norm over the whole q (k) projection ->
+// rotary -> q to scratch, k / v into the sequence's pages.  One block per token.
+template <class T>
+__global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const T* __restrict__ Uk, const T* __restrict__ Uv,
+                            const T* __restrict__ cwq, const T* __restrict__ cwk, const T* __restrict__ cwv, const T* __restrict__ nq,
+                            const T* __restrict__ nk, const T* __restrict__ cstate, size_t slot_stride, T* __restrict__ qout,
+                            T* __restrict__ kpool, T* __restrict__ vpool) {
+  extern __shared__ float sm[];
+  // a layer that borrows its keys and values projects and carries q only
+  const int Cq = a.H * a.dk, Ck = a.own_kv ? a.G * a.dk : 0, Cv = a.own_kv ? a.G * a.dv : 0, ldst = Cq + Ck + Cv;
+  float* qs = sm;
+  float* ks = sm + Cq;
+  float* red = ks + Ck;
+  const int n = blockIdx.x, slot = b.slot[n], p = b.pos[n];
+  const int local = n - b.first[n];   // rows of this step that precede the token in its sequence
+  const T* st = cstate + (size_t)slot * slot_stride;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < Cq; c += blockDim.x) {
+    const float v = conv_at(Uq, Cq, cwq, c, n, local, st, ldst, a.taps);
+    qs[c] = v;
+    sq += v * v;
+  }
+  sq = block_sum(sq, red);
+  if (a.own_kv) {
+    for (int c = threadIdx.x; c < Ck; c += blockDim.x) {
+      const float v = conv_at(Uk, Ck, cwk, c, n, local, st + Cq, ldst, a.taps);
+      ks[c] = v;
+      sk += v * v;
+    }
+    sk = block_sum(sk, red);
+  }
+  const float rq = 1.f / sqrtf(sq / (float)Cq + a.eps), rk = 1.f / sqrtf(sk / (float)Ck + a.eps);
+  const int page = b.bt[(size_t)slot * b.max_pages + p / PAGE], prow = p % PAGE;
+  const int halfk = a.dk / 2;
+  // pairs (2i, 2i+1) of every head; odd dk leaves its last dim to the tail loop below
+  for (int e = threadIdx.x; e < (a.H + (a.own_kv ? a.G : 0)) * halfk; e += blockDim.x) {
+    const int hh = e / halfk, i = e % halfk;
+    const bool isq = hh < a.H;
+    const int head = isq ? hh : hh - a.H;
+    const int c0 = head * a.dk + 2 * i;
+    float x0, x1;
+    if (isq) { x0 = qs[c0] * rq * ldf(nq + c0); x1 = qs[c0 + 1] * rq * ldf(nq + c0 + 1); }
+    else { x0 = ks[c0] * rk * ldf(nk + c0); x1 = ks[c0 + 1] * rk * ldf(nk + c0 + 1); }
+    if (2 * i + 1 < a.rot) {
+      const float ang = (float)p * a.inv_freq[i];
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+      const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
+      x0 = y0; x1 = y1;
+    }
+    if (isq) { stf(qout + (size_t)n * Cq + c0, x0); stf(qout + (size_t)n * Cq + c0 + 1, x1); }
+    else {
+      T* kr = kpool + ((size_t)page * PAGE + prow) * Ck;
+      stf(kr + c0, x0); stf(kr + c0 + 1, x1);
+    }
+  }
+  if (a.dk & 1) {
+    for (int hh = threadIdx.x; hh < a.H + (a.own_kv ? a.G : 0); hh += blockDim.x) {
+      const bool isq = hh < a.H;
+      const int c = (isq ? hh : hh - a.H) * a.dk + a.dk - 1;
+      if (isq) stf(qout + (size_t)n * Cq + c, qs[c] * rq * ldf(nq + c));
+      else stf(kpool + ((size_t)page * PAGE + prow) * Ck + c, ks[c] * rk * ldf(nk + c));
+    }
+  }
+  if (a.own_kv) {
+    T* vr = vpool + ((size_t)page * PAGE + prow) * Cv;
+    for (int c = threadIdx.x; c < Cv; c += blockDim.x)
+      stf(vr + c, conv_at(Uv, Cv, cwv, c, n, local, st + Cq + Ck, ldst, a.taps));
+  }
+}
+
+// paged attention of one (token, head): keys lo..p with lo the start of the query's block of `chunk` positions
+// (0: the sequence's start); fp32 scores, online softmax over 32-key tiles, fixed order.  One warp per block.
+template <class T>
+__global__ void __launch_bounds__(32) k_attn(Batch b, const T* __restrict__ q, const T* __restrict__ kpool, const T* __restrict__ vpool,
+                                             int H, int G, int dk, int dv, int chunk, float scale, T* __restrict__ out) {
+  extern __shared__ float sm[];
+  float* qs = sm;   // [dk]
+  const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+  const int g = h / (H / G), slot = b.slot[n], p = b.pos[n];
+  const int lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  const int Ck = G * dk, Cv = G * dv;
+  for (int d = lane; d < dk; d += 32) qs[d] = ldf(q + ((size_t)n * H + h) * dk + d);
+  __syncwarp();
+  const int32_t* bt = b.bt + (size_t)slot * b.max_pages;
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  for (int j0 = lo; j0 <= p; j0 += 32) {
+    const int j = j0 + lane;
+    float s = -INFINITY;
+    if (j <= p) {
+      const T* kr = kpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Ck + g * dk;
+      float d0 = 0.f;
+      for (int d = 0; d < dk; d++) d0 = fmaf(qs[d], ldf(kr + d), d0);
+      s = d0 * scale;
+    }
+    const float mn = fmaxf(m, warp_max(s));
+    const float corr = expf(m - mn);      // exp(-inf) = 0 on the first tile
+    const float pj = j <= p ? expf(s - mn) : 0.f;
+    l = l * corr + warp_sum(pj);
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] *= corr;
+    const int cnt = min(32, p - j0 + 1);
+    for (int t = 0; t < cnt; t++) {
+      const float pt = __shfl_sync(0xffffffffu, pj, t);
+      const int jj = j0 + t;
+      const T* vr = vpool + ((size_t)bt[jj / PAGE] * PAGE + (jj % PAGE)) * Cv + g * dv;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int d = lane + 32 * i;
+        if (d < dv) acc[i] = fmaf(pt, ldf(vr + d), acc[i]);
+      }
+    }
+    m = mn;
+  }
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int d = lane + 32 * i;
+    if (d < dv) stf(out + ((size_t)n * H + h) * dv + d, acc[i] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// gated delta rule
+struct DeltaPrep {
+  int H, G, dk, dv, taps;
+};
+// conv + silu on q, k, v; unit-norm q (times dk^-1/2) and k per head; beta = sigmoid(b), decay = exp(-exp(A) softplus(a + dt))
+template <class T>
+__global__ void k_delta_prep(DeltaPrep a, Batch b, const T* __restrict__ Uq, const T* __restrict__ Uk, const T* __restrict__ Uv,
+                             const T* __restrict__ cwq, const T* __restrict__ cwk, const T* __restrict__ cwv, const float* __restrict__ pa,
+                             const float* __restrict__ pb, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
+                             const T* __restrict__ cstate, size_t slot_stride, float* __restrict__ qn, float* __restrict__ kn,
+                             float* __restrict__ vv, float* __restrict__ beta, float* __restrict__ decay) {
+  extern __shared__ float sm[];
+  const int Cq = a.G * a.dk, Cv = a.H * a.dv, ldst = 2 * Cq + Cv;
+  float* qs = sm;
+  float* ks = sm + Cq;
+  const int n = blockIdx.x, slot = b.slot[n], p = b.pos[n];
+  const int local = n - b.first[n];
+  const T* st = cstate + (size_t)slot * slot_stride;
+  for (int c = threadIdx.x; c < Cq; c += blockDim.x) {
+    qs[c] = silu_f(conv_at(Uq, Cq, cwq, c, n, local, st, ldst, a.taps));
+    ks[c] = silu_f(conv_at(Uk, Cq, cwk, c, n, local, st + Cq, ldst, a.taps));
+  }
+  for (int c = threadIdx.x; c < Cv; c += blockDim.x) {
+    vv[(size_t)n * Cv + c] = silu_f(conv_at(Uv, Cv, cwv, c, n, local, st + 2 * Cq, ldst, a.taps));
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int hh = w; hh < 2 * a.G; hh += nw) {
+    const bool isq = hh < a.G;
+    const int g = isq ? hh : hh - a.G;
+    const float* src = (isq ? qs : ks) + g * a.dk;
+    float ss = 0.f;
+    for (int d = lane; d < a.dk; d += 32) ss += src[d] * src[d];
+    ss = warp_sum(ss);
+    const float r = (1.f / sqrtf(ss + 1e-6f)) * (isq ? 1.f / sqrtf((float)a.dk) : 1.f);
+    float* dst = (isq ? qn : kn) + (size_t)n * Cq + g * a.dk;
+    for (int d = lane; d < a.dk; d += 32) dst[d] = src[d] * r;
+  }
+  for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+    beta[(size_t)n * a.H + h] = 1.f / (1.f + expf(-pb[(size_t)n * a.H + h]));
+    decay[(size_t)n * a.H + h] = expf(-expf(ldf(A_log + h)) * softplus_f(pa[(size_t)n * a.H + h] + ldf(dt_bias + h)));
+  }
+}
+
+// The recurrence, token by token:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+// Columns of S are independent: a block owns 32 columns of one (entry, head); P adjacent lanes share a column,
+// each holding R = ceil(dk / P) of its rows in registers.  State [slot][head][dk][dv] fp32.
+template <int R>
+__global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, const float* __restrict__ qn, const float* __restrict__ kn,
+                             const float* __restrict__ vv, const float* __restrict__ beta, const float* __restrict__ decay,
+                             float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+  const int e = blockIdx.x / H, h = blockIdx.x % H, g = h / (H / G);
+  const int part = threadIdx.x % P, col = blockIdx.y * 32 + threadIdx.x / P;
+  const int s0 = b.ent_start[e], s1 = b.ent_start[e + 1];
+  const bool live = col < dv;
+  float* Sg = state + (size_t)b.ent_slot[e] * slot_stride + (size_t)h * dk * dv;
+  const int r0 = part * R;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; r++) S[r] = (live && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col] : 0.f;
+  const int Cq = G * dk, Cv = H * dv;
+  for (int n = s0; n < s1; n++) {
+    const float* kr = kn + (size_t)n * Cq + g * dk + r0;
+    const float* qr = qn + (size_t)n * Cq + g * dk + r0;
+    const float gd = decay[(size_t)n * H + h], bt = beta[(size_t)n * H + h];
+    const float v = live ? vv[(size_t)n * Cv + h * dv + col] : 0.f;
+    float kk[R];
+    float dot = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      kk[r] = r0 + r < dk ? kr[r] : 0.f;
+      S[r] *= gd;
+      dot = fmaf(S[r], kk[r], dot);
+    }
+    for (int x = 1; x < P; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+    const float u = bt * (v - dot);
+    float od = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      S[r] = fmaf(kk[r], u, S[r]);
+      od = fmaf(S[r], r0 + r < dk ? qr[r] : 0.f, od);
+    }
+    for (int x = 1; x < P; x <<= 1) od += __shfl_xor_sync(0xffffffffu, od, x);
+    if (live && part == 0) o[(size_t)n * Cv + h * dv + col] = od;
+  }
+#pragma unroll
+  for (int r = 0; r < R; r++)
+    if (live && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col] = S[r];
+}
+
+// read-out of the recurrence: per head o / rms(o) * w * silu(gate) -> T.  One warp per (token, head).
+template <class T>
+__global__ void __launch_bounds__(32) k_delta_out(const float* __restrict__ o, const T* __restrict__ gate, const T* __restrict__ nw, int H,
+                                                  int dv, float eps, T* __restrict__ out) {
+  const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+  const size_t base = ((size_t)n * H + h) * dv;
+  float ss = 0.f;
+  for (int d = lane; d < dv; d += 32) ss += o[base + d] * o[base + d];
+  ss = warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int d = lane; d < dv; d += 32) stf(out + base + d, o[base + d] * r * ldf(nw + d) * silu_f(ldf(gate + base + d)));
+}
+
+}  // namespace dnseq

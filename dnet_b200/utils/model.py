@@ -26,6 +26,9 @@ EMBED_TOKENS_RE = re.compile(r"^model\.embed_tokens\.(.+)$")
 LAYERS_RE = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
 LM_HEAD_RE = re.compile(r"^lm_head\.(.+)$")
 NORM_RE = re.compile(r"^model\.norm\.(.+)$")
+# checkpoints of the layer-list families (core/models/seqmix.py): l<i>.<tensor>, embed, final.norm, head
+SEQ_LAYER_RE = re.compile(r"^l(\d+)\.(.+)$")
+SEQ_API = {"embed": "embed_tokens", "final.norm": "norm", "head": "lm_head"}
 
 
 def get_model_layer_name(layer_idx: int, name: str) -> str:
@@ -91,7 +94,12 @@ class ModelMetadata:
 
     @cached_property
     def model_type(self) -> str:
-        return self.config["model_type"]
+        mt = self.config.get("model_type")
+        if mt is None and self.config.get("architecture"):
+            mt = str(self.config["architecture"]).lower()      # layer-list configs name their family this way
+        if mt is None:
+            raise KeyError("model_type")
+        return mt
 
     @property
     def model_config(self) -> Any:
@@ -127,6 +135,11 @@ def _classify(details: Dict[str, TensorInfo], weight_info, embed_tokens, lm_head
         elif m := LAYERS_RE.match(key):
             layer_idx, suffix = m.groups()
             weight_info[int(layer_idx)][suffix] = val
+        elif m := SEQ_LAYER_RE.match(key):
+            layer_idx, suffix = m.groups()
+            weight_info[int(layer_idx)][suffix] = val
+        elif key in SEQ_API:
+            {"embed_tokens": embed_tokens, "norm": norm, "lm_head": lm_head}[SEQ_API[key]]["weight"] = val
         else:
             raise RuntimeError(f"Unexpected key {key}")
 

@@ -1,0 +1,93 @@
+/*
+ * dnet_b200_seq.h -- C ABI of libdnet_b200_seq.so: the batched step of decoder models whose layers are a
+ * sequence mixer (chunk-masked softmax attention over a paged cache, or a gated delta-rule recurrence) plus an
+ * optional gated feed-forward, tied together by S residual streams.
+ *
+ * Same conventions as dnet_b200.h: plain C, opaque handles, 0 or a negative DN_E* code, dn_seq_last_error() for
+ * the text, caller-owned streams and buffers, weights BORROWED by pointer.  One handle serves one compute thread.
+ *
+ * A model holds a pool of 64-token cache pages and `max_seqs` state slots.  A sequence is opened into a slot, fed
+ * by dn_seq_step in portions of any size next to other sequences, and closed; its pages and slot are then reused.
+ */
+#ifndef DNET_B200_SEQ_H
+#define DNET_B200_SEQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DN_SEQ_BF16 0
+#define DN_SEQ_F32 1
+
+#define DN_MIX_ATTENTION 0
+#define DN_MIX_DELTA 1
+
+typedef struct dn_seq_model dn_seq_model;
+typedef void* dn_seq_stream;   /* cudaStream_t */
+
+typedef struct dn_seq_layer_cfg {
+  int32_t mixer;       /* DN_MIX_* */
+  int32_t heads;       /* query heads (attention) / value heads (delta) */
+  int32_t kv_heads;    /* key/value heads (attention) / query-key heads (delta) */
+  int32_t dim;         /* per-head query/key size */
+  int32_t vdim;        /* per-head value size */
+  int32_t conv;        /* taps of the short causal convolution on q, k, v (0: none) */
+  int32_t chunk;       /* attention: a query sees its own block of this many positions (0: plain causal) */
+  int32_t rot_dims;    /* attention: rotated dims per head (0: none) */
+  float rot_base;
+  float scale;         /* attention: score scale */
+  int32_t kv_from;     /* attention: layer whose pages hold this layer's keys and values (-1: its own) */
+  int32_t ff;          /* feed-forward width (0: the layer has no feed-forward) */
+} dn_seq_layer_cfg;
+
+typedef struct dn_seq_cfg {
+  int32_t width, vocab, n_layers;
+  int32_t streams;           /* residual streams (0: plain residual) */
+  int32_t dtype;             /* DN_SEQ_BF16: bf16 storage, fp32 sums;  DN_SEQ_F32: everything fp32 */
+  float eps;                 /* of every RMS norm */
+  float embed_scale;
+  int32_t pool_pages;        /* 64-token pages in the cache pool */
+  int32_t max_seqs;          /* state slots */
+  int32_t max_batch_tokens;  /* most tokens one dn_seq_step may bring */
+} dn_seq_cfg;
+
+/* tensors of a layer (dn_seq_bind: layer >= 0) and of the model (layer = -1) */
+enum {
+  DN_SQ_NORM1 = 0, DN_SQ_NORM2,
+  DN_SQ_Q, DN_SQ_K, DN_SQ_V, DN_SQ_O, DN_SQ_Q_CONV, DN_SQ_K_CONV, DN_SQ_V_CONV, DN_SQ_Q_NORM, DN_SQ_K_NORM,
+  DN_SQ_A, DN_SQ_B, DN_SQ_G, DN_SQ_A_LOG, DN_SQ_DT_BIAS, DN_SQ_OUT_NORM,
+  DN_SQ_GATE, DN_SQ_UP, DN_SQ_DOWN,
+  DN_SQ_HC1_IN, DN_SQ_HC1_OUT, DN_SQ_HC1_MIX, DN_SQ_HC2_IN, DN_SQ_HC2_OUT, DN_SQ_HC2_MIX,
+  DN_SQ_COUNT,
+  DN_SQ_EMBED = 100, DN_SQ_FINAL_NORM, DN_SQ_HEAD
+};
+
+int dn_seq_init(int device);
+const char* dn_seq_last_error(void);
+int64_t dn_seq_launch_count(void);
+
+int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg* layers, dn_seq_model** out);
+int dn_seq_model_destroy(dn_seq_model* m);
+int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* dev_ptr);
+
+/* sequences: open takes a free state slot (zeroed behind the work queued on s); close returns slot and pages */
+int dn_seq_open(dn_seq_model* m, dn_seq_stream s, int* slot_out);
+int dn_seq_close(dn_seq_model* m, int slot);
+int dn_seq_length(dn_seq_model* m, int slot);
+int dn_seq_free_pages(dn_seq_model* m);
+int dn_seq_free_slots(dn_seq_model* m);
+
+/* One step: entry e brings counts[e] tokens (concatenated in tokens_host) of the sequence in slots[e]; the rows
+ * want_host[0..n_want) of the concatenation get logits, written as fp32 [n_want, vocab] to logits_dev.
+ * layer_trace_dev (optional): fp32 [n_layers, N, width], the residual (sum of the streams) after every layer.
+ * Asynchronous on s except for the staging of the previous step's arguments. */
+int dn_seq_step(dn_seq_model* m, int n_entries, const int32_t* slots, const int32_t* counts, const int32_t* tokens_host,
+                int n_want, const int32_t* want_host, float* logits_dev, float* layer_trace_dev, dn_seq_stream s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
