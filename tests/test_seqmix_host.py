@@ -1,0 +1,152 @@
+"""Host-side pieces of the layer-list families that need no GPU: config parsing, checkpoint naming, the oracle's
+own mechanisms against independent formulations, and the batcher's token loop over a fake model."""
+from __future__ import annotations
+
+import torch
+
+from oracle import seqmix_oracle as so
+
+CFG = {"architecture": "Moputar", "vocab": 50, "width": 32, "streams": 2, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+       "layers": [
+           {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "conv": 3, "scale": 0.3,
+                                           "rot": {"base": 777.0, "dims": 4}, "mask": {"size": 11}}, "mlp": {"kind": "dense", "ff": 40}},
+           {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "conv": 3, "scale": 0.3, "kv_from": 0,
+                                           "rot": {"base": 777.0, "dims": 4}, "mask": {"size": 11}}, "mlp": None},
+           {"type": "delta", "mixer": {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 16, "conv": 2}, "mlp": None}]}
+
+
+def test_config_to_structs():
+    from dnet_b200 import _seqabi
+    from dnet_b200.core.models.seqmix import parse_layer_list
+
+    sc, layers = parse_layer_list(CFG)
+    assert (sc.width, sc.vocab, sc.n_layers, sc.streams) == (32, 50, 3, 2)
+    assert abs(sc.eps - 1e-5) < 1e-12 and sc.embed_scale == 2.0
+    a, b, d = layers
+    assert (a.mixer, a.heads, a.kv_heads, a.dim, a.vdim, a.conv, a.chunk, a.rot_dims, a.kv_from, a.ff) == \
+        (_seqabi.DN_MIX_ATTENTION, 4, 2, 8, 12, 3, 11, 4, -1, 40)
+    assert abs(a.rot_base - 777.0) < 1e-3 and abs(a.scale - 0.3) < 1e-7
+    assert b.kv_from == 0 and b.ff == 0
+    assert (d.mixer, d.heads, d.kv_heads, d.dim, d.vdim, d.conv, d.ff) == (_seqabi.DN_MIX_DELTA, 2, 1, 8, 16, 2, 0)
+    # absent keys switch the mechanism off
+    bare = {"vocab": 5, "width": 8, "layers": [{"type": "attention", "mixer": {"heads": 2, "dim": 4}, "mlp": None}]}
+    sc, (l0,) = parse_layer_list(bare)
+    assert (sc.streams, l0.kv_heads, l0.vdim, l0.conv, l0.chunk, l0.rot_dims, l0.kv_from) == (0, 2, 4, 0, 0, 0, -1)
+    assert abs(l0.scale - 0.5) < 1e-7
+
+
+def test_checkpoint_names_reach_the_registry():
+    from dnet_b200.core.models import MoputarRingModel, SeqMixRingModel
+    from dnet_b200.utils.model import HostDictSource, get_model_metadata
+
+    w = so.random_weights(CFG, 0)
+    md = get_model_metadata(HostDictSource(w, CFG))
+    assert md.model_type == "moputar" and md.num_layers == 3
+    assert set(md.weight_info[1]) == {"norm1", "mix.q", "mix.q.conv", "mix.q.norm", "mix.o", "hc1.in", "hc1.out", "hc1.mix"}
+    assert md.embed_tokens["weight"].shape == (50, 32) and md.norm["weight"].shape == (32,) and md.lm_head["weight"].shape == (50, 32)
+    assert MoputarRingModel.model_type == "moputar" and issubclass(MoputarRingModel, SeqMixRingModel)
+    assert set(so.tensor_shapes(CFG)) == set(w)
+
+
+def test_header_and_binding_agree():
+    from dnet_b200 import _seqabi
+
+    assert set(_seqabi.declared_symbols()) == set(_seqabi._PROTOS)
+    txt = _seqabi.HEADER_PATH.read_text()
+    order = [n.strip() for n in txt.split("enum {", 1)[1].split("DN_SQ_COUNT", 1)[0].replace("= 0", "").replace("\n", " ").split(",") if n.strip()]
+    assert len(order) == len(_seqabi.LAYER_SLOT)
+    spell = {"OUT_NORM": "mix.norm", "NORM1": "norm1", "NORM2": "norm2", "GATE": "mlp.gate", "UP": "mlp.up", "DOWN": "mlp.down"}
+    for i, name in enumerate(order):
+        n = name[len("DN_SQ_"):]
+        want = spell.get(n) or (n.lower().replace("_", ".", 1) if n.startswith("HC") else "mix." + {"A_LOG": "A_log", "DT_BIAS": "dt_bias"}.get(n, n.lower().replace("_", ".")))
+        assert _seqabi.LAYER_SLOT[want] == i, (name, want)
+
+
+def test_oracle_conv_is_a_causal_depthwise_fir():
+    g = torch.Generator().manual_seed(0)
+    u, w = torch.randn(9, 5, generator=g, dtype=torch.float64), torch.randn(5, 3, generator=g, dtype=torch.float64)
+    ref = torch.nn.functional.conv1d(torch.nn.functional.pad(u.T[None], (2, 0)), w[:, None, :], groups=5)[0].T
+    assert torch.allclose(so.short_conv(u, w), ref, atol=1e-12)
+    assert torch.equal(so.short_conv(u, None), u)
+
+
+def test_oracle_delta_rule_writes_and_reads_back():
+    # with no decay and beta = 1 an orthonormal key's value is stored exactly and replaced exactly
+    k = torch.eye(4, dtype=torch.float64)[[0, 1, 0]]
+    v = torch.tensor([[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]], dtype=torch.float64)
+    o = so.delta_rule(k, k, v, torch.ones(3, dtype=torch.float64), torch.ones(3, dtype=torch.float64))
+    assert torch.allclose(o, v)
+    # decay scales what was stored before the current write
+    o = so.delta_rule(torch.eye(4, dtype=torch.float64)[[0, 0]], k[:2], v[:2], torch.zeros(2, dtype=torch.float64).add(1.0),
+                      torch.tensor([1.0, 0.5], dtype=torch.float64))
+    assert torch.allclose(o[1], 0.5 * v[0])
+
+
+def test_oracle_block_mask_and_rotation():
+    ok = so.visible(7, 3)
+    assert ok[5].tolist() == [False, False, False, True, True, True, False] and ok[3].tolist() == [False] * 3 + [True] + [False] * 3
+    assert so.visible(4, 0).tolist() == torch.ones(4, 4).tril().bool().tolist()
+    z = torch.randn(5, 2, 6, dtype=torch.float64)
+    r = so.rotate_pairs(z, torch.arange(5), 4, 100.0)
+    assert torch.equal(r[..., 4:], z[..., 4:]) and torch.allclose(r[0], z[0])
+    assert torch.allclose(r.pow(2).sum(-1), z.pow(2).sum(-1))
+    # scores depend on the distance only
+    q, k = torch.randn(1, 1, 4, dtype=torch.float64), torch.randn(1, 1, 4, dtype=torch.float64)
+    s = [float((so.rotate_pairs(q, torch.tensor([a]), 4, 100.0) * so.rotate_pairs(k, torch.tensor([a - 3]), 4, 100.0)).sum()) for a in (3, 50)]
+    assert abs(s[0] - s[1]) < 1e-9
+
+
+class _FakeHandle:
+    def __init__(self, m):
+        self.m, self.offset, self.slot = m, 0, m.slots.pop()
+
+    def free(self):
+        self.m.slots.append(self.slot)
+        self.m.pages += (self.offset + 63) // 64
+
+
+class _FakeModel:
+    """counts tokens; its 'logits' make the greedy token (last token + 1) mod vocab"""
+    max_batch_tokens, vocab_size, pool_pages = 32, 17, 6
+
+    def __init__(self):
+        self.slots, self.pages, self.steps = [1, 0], 6, []
+
+    free_slots = property(lambda s: len(s.slots))
+    free_pages = property(lambda s: s.pages)
+
+    def make_cache(self, stream=None):
+        return _FakeHandle(self)
+
+    def step(self, entries, want, stream=None, layer_trace=False):
+        rows = []
+        for h, t in entries:
+            self.pages -= (h.offset + len(t) + 63) // 64 - (h.offset + 63) // 64
+            h.offset += len(t)
+            rows += list(t)
+        self.steps.append([len(t) for _, t in entries])
+        assert sum(self.steps[-1]) <= self.max_batch_tokens and self.pages >= 0
+        out = torch.zeros(len(want), self.vocab_size)
+        for i, r in enumerate(want):
+            out[i, (rows[r] + 1) % self.vocab_size] = 1.0
+        return out
+
+
+def test_token_loop_schedules_decodes_beside_prompt_portions(monkeypatch):
+    from dnet_b200.shard import batching
+
+    class _S:
+        def synchronize(self): pass
+        def wait_stream(self, s): pass
+
+    import contextlib
+    monkeypatch.setattr(batching.torch.cuda, "stream", lambda s: contextlib.nullcontext())
+    monkeypatch.setattr(batching.torch.cuda, "current_stream", lambda: _S())
+    m = _FakeModel()
+    eng = batching.SequenceBatcher(m, stream=_S(), step_tokens=16)
+    reqs = [batching.GenRequest("a", [1, 2, 3], 4), batching.GenRequest("b", list(range(40)), 3), batching.GenRequest("c", [9] * 70, 2)]
+    out = eng.generate(reqs)
+    assert out == {"a": [4, 5, 6, 7], "b": [6, 7, 8], "c": [10, 11]}
+    assert all(sum(s) <= 16 for s in m.steps)
+    assert any(len(s) == 2 and 1 in s and max(s) > 1 for s in m.steps)      # a decode token beside a prompt portion
+    assert m.free_slots == 2 and m.free_pages == 6                             # everything was handed back
