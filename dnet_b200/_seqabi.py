@@ -21,6 +21,9 @@ _LAYER_SLOTS = ["norm1", "norm2", "mix.q", "mix.k", "mix.v", "mix.o", "mix.q.con
                 "hc1.in", "hc1.out", "hc1.mix", "hc2.in", "hc2.out", "hc2.mix"]
 LAYER_SLOT = {n: i for i, n in enumerate(_LAYER_SLOTS)}
 MODEL_SLOT = {"embed": 100, "final.norm": 101, "head": 102}
+# phases of a step, in the header's order (dn_seq_profile_read)
+PHASES = ["embed", "norm", "proj", "attn_prep", "attn", "delta_prep", "delta_rule", "delta_out", "conv_carry", "out_proj",
+          "write_back", "ff_up", "ff_down", "head", "other"]
 
 
 class LayerCfg(C.Structure):
@@ -54,6 +57,9 @@ _PROTOS = {
     "dn_seq_length": (_i, [_vp, _i]),
     "dn_seq_free_pages": (_i, [_vp]),
     "dn_seq_free_slots": (_i, [_vp]),
+    "dn_seq_check": (_i, [_vp, _vp]),
+    "dn_seq_profile": (_i, [_vp, _i]),
+    "dn_seq_profile_read": (_i, [_vp, C.POINTER(C.c_double), _i]),
     "dn_seq_step": (_i, [_vp, _i, _I32P, _I32P, _I32P, _i, _I32P, _vp, _vp, _vp]),
 }
 _lib = None

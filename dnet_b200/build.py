@@ -11,9 +11,10 @@ SRC = ROOT / "csrc" / "dn_api.cu"
 # the batched sequence-mixer step is a library of its own: a process that serves such a model compiles and loads
 # only this one
 SEQ_SRC = ROOT / "csrc" / "dn_seq.cu"
-SEQ_DEPS = [*sorted((ROOT / "csrc").glob("dn_seq*.cu*")), ROOT.parent / "include" / "dnet_b200_seq.h"]
+_SEQ_ONLY = [*sorted((ROOT / "csrc").glob("dn_seq*.cu*")), ROOT.parent / "include" / "dnet_b200_seq.h"]
+SEQ_DEPS = [*_SEQ_ONLY, *sorted((ROOT / "csrc").glob("*.cuh"))]      # it shares the tcgen05 GEMM of dn_gemm_tc.cuh
 SEQ_OUT = ROOT / "lib" / "libdnet_b200_seq.so"
-DEPS = [d for d in [*sorted((ROOT / "csrc").glob("*.cu*")), ROOT.parent / "include" / "dnet_b200.h"] if d not in SEQ_DEPS]
+DEPS = [d for d in [*sorted((ROOT / "csrc").glob("*.cu*")), ROOT.parent / "include" / "dnet_b200.h"] if d not in _SEQ_ONLY]
 OUT = ROOT / "lib" / "libdnet_b200.so"
 
 NVCC_FLAGS = [

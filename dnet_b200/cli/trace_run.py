@@ -40,7 +40,7 @@ def main(argv=None) -> int:
         entries = [(str(e["id"]), e["tokens"], e.get("want") or []) for e in st.get("entries", []) if e.get("tokens")]
         logits = eng.step(entries) if entries else None
         if logits is not None:
-            eng.stream.synchronize()
+            model.check(eng.stream)
             data = logits.to("cpu", torch.float32).contiguous().numpy().astype("<f4", copy=False).tobytes()
             tmp = os.path.join(a.out, ".%s.part" % st["step"])
             with open(tmp, "wb") as f:

@@ -230,6 +230,20 @@ class SeqMixRingModel(BaseRingModel):
                                             trace.data_ptr() if layer_trace else None, _stream_ptr(stream)))
         return (logits, trace) if layer_trace else logits
 
+    def check(self, stream=None) -> None:
+        """Synchronise and raise if a bounded wait inside a kernel ever ran out (results would be invalid)."""
+        _seqabi.check(self._lib.dn_seq_check(self._h, _stream_ptr(stream)))
+
+    def profile(self, on: bool) -> None:
+        """Switch the per-phase device timers of the step on or off."""
+        _seqabi.check(self._lib.dn_seq_profile(self._h, int(bool(on))))
+
+    def profile_read(self, reset: bool = True) -> Dict[str, float]:
+        """Milliseconds per phase over the steps run since the last read (synchronises)."""
+        ms = (C.c_double * len(_seqabi.PHASES))()
+        _seqabi.check(self._lib.dn_seq_profile_read(self._h, ms, int(bool(reset))))
+        return {n: float(ms[i]) for i, n in enumerate(_seqabi.PHASES)}
+
     # -- BaseRingModel surface ---------------------------------------------------------------------
     def _whole(self, *_a, **_k):
         raise NotImplementedError("layer-list models run whole batched steps (SeqMixRingModel.step); the residual between "

@@ -742,7 +742,7 @@ static int head_common(dn_model* m, const void* x, int T, dn_kv* kv, int32_t* to
 // ---- tensor-core prefill path (16 <= T <= TPF_MAX): tcgen05 GEMMs fed by TMA (dn_gemm_tc.cuh)
 template <int BN, int EPI, int STAGES>
 static cudaError_t launch_tc(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, const TcParams& p, cudaStream_t s) {
-  constexpr int NA = (EPI == EPI_SWIGLU) ? 2 : 1;
+  constexpr int NA = epi_two_weights(EPI) ? 2 : 1;
   constexpr size_t smem = (size_t)STAGES * (NA * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
   static bool attr = false;
   if (!attr) {

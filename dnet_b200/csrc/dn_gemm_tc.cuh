@@ -15,13 +15,18 @@
 //   EPI_RESID  : y = T(resid[t][n] + T(acc))              -> Y[t][n]
 //   EPI_SWIGLU : two weight tiles (gate, up) share the token tile; g = T(acc_g), u = T(acc_u),
 //                s = T(sigmoid g), a = T(g s), m = T(a u)  -> Y[t][n]
+//   EPI_STORE_F32 : the fp32 accumulator itself               -> ((float*)Y)[t][col0 + n]   (outputs that join an fp32
+//                residual or feed fp32 gates)
+//   EPI_GEGLU  : two weight tiles like EPI_SWIGLU; y = T(gelu_tanh(acc_g) * acc_u), the activation and the product
+//                in fp32 with one rounding                     -> Y[t][n]
 #pragma once
 #include <cuda.h>
 #include "dn_megakernel.cuh"
 
 namespace dn {
 
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_GEGLU = 4 };
+__host__ __device__ constexpr bool epi_two_weights(int epi) { return epi == EPI_SWIGLU || epi == EPI_GEGLU; }
 
 constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
 constexpr int TC_BK = 64;         // k-step: 64 bf16 = 128 bytes = one swizzle span
@@ -92,7 +97,7 @@ template <int BN, int EPI, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapW2,
           const __grid_constant__ CUtensorMap mapX, const TcParams p) {
-  constexpr int NA = (EPI == EPI_SWIGLU) ? 2 : 1;
+  constexpr int NA = epi_two_weights(EPI) ? 2 : 1;
   constexpr int A_BYTES = TC_BM * TC_BK * 2;      // 16 KB
   constexpr int B_BYTES = BN * TC_BK * 2;
   constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES;
@@ -194,14 +199,21 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
       for (int c = 0; c < BN; c += 16) {
         float v[16], v2[16];
         tc_ld16(trow + c, v);
-        if (EPI == EPI_SWIGLU) tc_ld16(trow + BN + c, v2);
+        if (NA == 2) tc_ld16(trow + BN + c, v2);
         if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int t = tt * BN + c + j;
             if (t < p.T) {
+              if (EPI == EPI_STORE_F32) {
+                reinterpret_cast<float*>(p.Y)[(size_t)t * p.ldy + p.col0 + n] = v[j];
+                continue;
+              }
               float y;
-              if (EPI == EPI_STORE) {
+              if (EPI == EPI_GEGLU) {
+                const float g = v[j];
+                y = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * v2[j];
+              } else if (EPI == EPI_STORE) {
                 y = v[j] + bias;
               } else if (EPI == EPI_RESID) {
                 y = __fadd_rn(__bfloat162float(p.resid[(size_t)t * p.ldr + n]), bf16r(v[j]));

@@ -2,6 +2,7 @@
 // bound weight pointers, the page pool and the state slots, the staging of a step's batch description, and the
 // launch sequence of a layer.  All arithmetic is in dn_seq_kernels.cuh.
 #include "dn_seq_kernels.cuh"
+#include "dn_gemm_tc.cuh"      // the tcgen05 / TMA GEMM the llama-family prefill runs on (namespace dn)
 #include "../../include/dnet_b200_seq.h"
 
 #include <atomic>
@@ -10,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <type_traits>
 #include <vector>
 
 using namespace dnseq;
@@ -41,9 +43,17 @@ static int g_device = -1;
 static int g_sms = 0;
 static size_t g_max_smem = 0;
 
+// weight matrices and the activation buffers they multiply get TMA descriptors in bf16 mode
+struct XMaps {
+  CUtensorMap m[3];     // token tiles of 32 / 64 / 128 rows
+  bool ok = false;
+};
 struct SeqLayer {
   dn_seq_layer_cfg c;
   const void* w[DN_SQ_COUNT];
+  CUtensorMap tm[DN_SQ_COUNT];
+  bool tm_ok[DN_SQ_COUNT];
+  XMaps x_mo, x_act;            // the mixer's output buffer [MB, Co] and the feed-forward's [MB, ff]
   int Cq, Ck, Cv, Co;           // projection widths: q, k, v and the mixer's output before W_o
   int kv_index;                 // attention: which page pool (own or the one it borrows); -1 for delta
   size_t conv_off, delta_off;   // element offsets into a slot's carried conv inputs / fp32 delta state
@@ -69,6 +79,15 @@ struct dn_seq_model {
   std::vector<int> free_pages, free_slots;
   std::vector<std::vector<int>> pages;   // per slot
   std::vector<int> length;               // per slot, -1: closed
+  XMaps x_h;                    // the normed activations [MB, W]
+  CUtensorMap tm_head;
+  bool tm_head_ok = false;
+  unsigned int* tc_err = nullptr;   // set by a bounded in-kernel wait of the tcgen05 GEMM that ran out
+  // phase profiler (off by default): one event at every phase boundary of a step, read back by dn_seq_profile_read
+  bool prof_on = false;
+  std::vector<cudaEvent_t> prof_pool;
+  std::vector<std::pair<int, cudaEvent_t>> prof_marks;
+  double prof_ms[DN_SEQ_PH_COUNT] = {0};
   // staging
   int32_t *stage_h = nullptr, *stage_d = nullptr, *bt_h = nullptr, *bt_d = nullptr;
   size_t stage_ints = 0;
@@ -101,6 +120,34 @@ extern "C" int dn_seq_init(int device) {
   return DN_OK;
 }
 
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_encodeTiled g_encode = nullptr;
+// [rows, cols] bf16 row-major, box box_rows x 64 columns (one 128-byte swizzle span); false when the tensor cannot
+// have one (pitch or base not a multiple of 16 bytes) -- such products run on the CUDA-core kernels
+static bool make_tmap(CUtensorMap* out, const void* base, int rows, int cols, int box_rows) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+      return false;
+    g_encode = (PFN_encodeTiled)fn;
+  }
+  if (!base || cols % 64 || ((uintptr_t)base & 15)) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static void make_xmaps(XMaps* x, const void* base, int rows, int cols) {
+  x->ok = true;
+  const int br[3] = {32, 64, 128};
+  for (int i = 0; i < 3; i++) x->ok = x->ok && make_tmap(&x->m[i], base, rows, cols, br[i]);
+}
+
 template <class P>
 static int dalloc(P** p, size_t bytes) {
   void* q = nullptr;
@@ -113,8 +160,10 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   if (!m) return DN_OK;
   cudaDeviceSynchronize();
   void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
-                  m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d};
+                  m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err};
   for (void* p : ptrs) if (p) cudaFree(p);
+  for (auto& pm : m->prof_marks) cudaEventDestroy(pm.second);
+  for (cudaEvent_t ev : m->prof_pool) cudaEventDestroy(ev);
   for (void* p : m->kpool) if (p) cudaFree(p);
   for (void* p : m->vpool) if (p) cudaFree(p);
   for (auto& l : m->L) if (l.inv_freq) cudaFree(l.inv_freq);
@@ -147,6 +196,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
     SeqLayer& l = m->L[i];
     l.c = layers[i];
     memset(l.w, 0, sizeof(l.w));
+    memset(l.tm_ok, 0, sizeof(l.tm_ok));
     l.inv_freq = nullptr;
     l.kv_index = -1;
     const dn_seq_layer_cfg& c = l.c;
@@ -210,8 +260,16 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   DA(m->mo, MB * mo * e); DA(m->gt, MB * mo * e); DA(m->act, MB * mff * e);
   DA(m->conv_state, (size_t)cfg->max_seqs * coff * e); DA(m->delta_state, (size_t)cfg->max_seqs * doff * 4);
   m->stage_ints = 4 * MB + 3 * (size_t)(cfg->max_seqs + 1) + MB;
-  DA(m->stage_d, m->stage_ints * 4); DA(m->bt_d, (size_t)cfg->max_seqs * m->max_pages * 4);
+  DA(m->stage_d, m->stage_ints * 4); DA(m->bt_d, (size_t)cfg->max_seqs * m->max_pages * 4); DA(m->tc_err, 16);
 #undef DA
+  if (rc == DN_OK && cudaMemset(m->tc_err, 0, 16) != cudaSuccess) rc = fail(DN_ECUDA, "memset failed");
+  if (rc == DN_OK && cfg->dtype == DN_SEQ_BF16) {
+    make_xmaps(&m->x_h, m->h, m->MB, cfg->width);
+    for (auto& l : m->L) {
+      make_xmaps(&l.x_mo, m->mo, m->MB, l.Co);
+      if (l.c.ff > 0) make_xmaps(&l.x_act, m->act, m->MB, l.c.ff);
+    }
+  }
   if (rc == DN_OK && cudaHostAlloc((void**)&m->stage_h, m->stage_ints * 4, cudaHostAllocPortable) != cudaSuccess) rc = fail(DN_ENOMEM, "pinned staging failed");
   if (rc == DN_OK && cudaHostAlloc((void**)&m->bt_h, (size_t)cfg->max_seqs * m->max_pages * 4, cudaHostAllocPortable) != cudaSuccess) rc = fail(DN_ENOMEM, "pinned block table failed");
   if (rc == DN_OK && cudaEventCreateWithFlags(&m->staged, cudaEventDisableTiming) != cudaSuccess) rc = fail(DN_ECUDA, "event creation failed");
@@ -226,15 +284,32 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
 
 extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p) {
   if (!m) return fail(DN_EINVAL, "null model");
+  const bool b16 = m->cfg.dtype == DN_SEQ_BF16;
   if (layer < 0) {
     if (which == DN_SQ_EMBED) m->embed = p;
     else if (which == DN_SQ_FINAL_NORM) m->final_norm = p;
-    else if (which == DN_SQ_HEAD) m->head = p;
-    else return fail(DN_EINVAL, "tensor %d is not a model tensor", which);
+    else if (which == DN_SQ_HEAD) {
+      m->head = p;
+      m->tm_head_ok = b16 && make_tmap(&m->tm_head, p, m->cfg.vocab, m->cfg.width, dn::TC_BM);
+    } else return fail(DN_EINVAL, "tensor %d is not a model tensor", which);
     return DN_OK;
   }
   if (layer >= (int)m->L.size() || which < 0 || which >= DN_SQ_COUNT) return fail(DN_EINVAL, "layer %d / tensor %d out of range", layer, which);
-  m->L[layer].w[which] = p;
+  SeqLayer& l = m->L[layer];
+  l.w[which] = p;
+  int rows = 0, cols = m->cfg.width;
+  switch (which) {
+    case DN_SQ_Q: rows = l.Cq; break;
+    case DN_SQ_K: rows = l.Ck; break;
+    case DN_SQ_V: rows = l.Cv; break;
+    case DN_SQ_G: rows = l.Co; break;
+    case DN_SQ_A: case DN_SQ_B: rows = l.c.heads; break;
+    case DN_SQ_GATE: case DN_SQ_UP: rows = l.c.ff; break;
+    case DN_SQ_O: rows = m->cfg.width; cols = l.Co; break;
+    case DN_SQ_DOWN: rows = m->cfg.width; cols = l.c.ff; break;
+    default: break;
+  }
+  l.tm_ok[which] = b16 && rows > 0 && make_tmap(&l.tm[which], p, rows, cols, dn::TC_BM);
   return DN_OK;
 }
 
@@ -265,15 +340,99 @@ extern "C" int dn_seq_length(dn_seq_model* m, int slot) {
   if (!m || slot < 0 || slot >= m->cfg.max_seqs) return DN_EINVAL;
   return m->length[slot];
 }
+extern "C" int dn_seq_check(dn_seq_model* m, dn_seq_stream s) {
+  if (!m) return fail(DN_EINVAL, "null model");
+  unsigned int e = 0;
+  CK(cudaMemcpyAsync(&e, m->tc_err, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+  CK(cudaStreamSynchronize((cudaStream_t)s));
+  if (e) return fail(-62, "a bounded wait inside a GEMM kernel ran out (code %u): results of this model are invalid", e);
+  return DN_OK;
+}
+extern "C" int dn_seq_profile(dn_seq_model* m, int on) {
+  if (!m) return fail(DN_EINVAL, "null model");
+  m->prof_on = on != 0;
+  return DN_OK;
+}
+extern "C" int dn_seq_profile_read(dn_seq_model* m, double* ms_out, int reset) {
+  if (!m || !ms_out) return fail(DN_EINVAL, "bad argument");
+  CK(cudaDeviceSynchronize());
+  for (size_t i = 0; i + 1 < m->prof_marks.size(); i++) {
+    float ms = 0.f;
+    // a step's last mark closes it: the gap to the next step's first mark is host time, not a phase
+    if (m->prof_marks[i].first != DN_SEQ_PH_OTHER || m->prof_marks[i + 1].first != DN_SEQ_PH_EMBED) {
+      CK(cudaEventElapsedTime(&ms, m->prof_marks[i].second, m->prof_marks[i + 1].second));
+      m->prof_ms[m->prof_marks[i].first] += ms;
+    }
+  }
+  for (auto& pm : m->prof_marks) m->prof_pool.push_back(pm.second);
+  m->prof_marks.clear();
+  for (int i = 0; i < DN_SEQ_PH_COUNT; i++) ms_out[i] = m->prof_ms[i];
+  if (reset) for (int i = 0; i < DN_SEQ_PH_COUNT; i++) m->prof_ms[i] = 0;
+  return DN_OK;
+}
 extern "C" int dn_seq_free_pages(dn_seq_model* m) { return m ? (int)m->free_pages.size() : DN_EINVAL; }
 extern "C" int dn_seq_free_slots(dn_seq_model* m) { return m ? (int)m->free_slots.size() : DN_EINVAL; }
 
 // ---------------------------------------------------------------------------------------------------------------
+template <int BN, int EPI, int STAGES>
+static cudaError_t launch_tc(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, const dn::TcParams& p, cudaStream_t s) {
+  constexpr int NA = dn::epi_two_weights(EPI) ? 2 : 1;
+  constexpr size_t smem = (size_t)STAGES * (NA * dn::TC_BM * dn::TC_BK * 2 + BN * dn::TC_BK * 2) + 1024 + 256;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(dn::k_gemm_tc<BN, EPI, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  const int tiles = ((p.N + dn::TC_BM - 1) / dn::TC_BM) * ((p.T + BN - 1) / BN);
+  g_launches++;
+  dn::k_gemm_tc<BN, EPI, STAGES><<<tiles < g_sms ? tiles : g_sms, dn::TC_THREADS, smem, s>>>(w, w2, x, p);
+  return cudaGetLastError();
+}
+// token-tile width: the widest that still gives about one CTA per SM
+template <int EPI>
+static cudaError_t gemm_tc(const CUtensorMap& w, const CUtensorMap& w2, const XMaps& x, const dn::TcParams& p, cudaStream_t s) {
+  constexpr bool two = dn::epi_two_weights(EPI);
+  const int n_tiles = (p.N + dn::TC_BM - 1) / dn::TC_BM;
+  auto tiles = [&](int bn) { return n_tiles * ((p.T + bn - 1) / bn); };
+  if (p.T > 64 && tiles(128) >= 100) return launch_tc<128, EPI, (two ? 4 : 6)>(w, w2, x.m[2], p, s);
+  if (p.T > 32 && (tiles(64) >= 100 || tiles(64) * 2 > tiles(32))) return launch_tc<64, EPI, (two ? 5 : 8)>(w, w2, x.m[1], p, s);
+  return launch_tc<32, EPI, (two ? 5 : 8)>(w, w2, x.m[0], p, s);
+}
+
+// One product Y[N, O] = X[N, K] W[O, K]^T (act: gelu_tanh(X W^T) * (X W2^T)).  bf16 batches of 16 tokens and more run on
+// the tcgen05 GEMM when the operands have TMA descriptors; a few rows (decode) on the weight-streaming row kernel;
+// everything else, and all of fp32, on the CUDA-core tiles.
+struct LinMaps { const CUtensorMap* w; const CUtensorMap* w2; const XMaps* x; };
 template <class T>
-static cudaError_t linear(cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32, int act) {
+static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32,
+                          int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}) {
+  if (std::is_same<T, bf16>::value && N >= 16 && O >= 32 && tm.w && tm.x && tm.x->ok && (!act || tm.w2)) {
+    dn::TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err;
+    if (act) return gemm_tc<dn::EPI_GEGLU>(*tm.w, *tm.w2, *tm.x, p, s);
+    if (out32) return gemm_tc<dn::EPI_STORE_F32>(*tm.w, *tm.w, *tm.x, p, s);
+    return gemm_tc<dn::EPI_STORE>(*tm.w, *tm.w, *tm.x, p, s);
+  }
+  if (N <= 8) {
+    dim3 grid((O + 7) / 8);
+    if (out32) return launch(k_linear_rows<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
+    return launch(k_linear_rows<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
+  }
   dim3 grid((O + 63) / 64, (N + 63) / 64);
   if (out32) return launch(k_linear<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
   return launch(k_linear<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
+}
+
+// phase boundary: the time from this mark to the next one is booked on `phase`
+static cudaError_t mark(dn_seq_model* m, int phase, cudaStream_t s) {
+  if (!m->prof_on) return cudaSuccess;
+  cudaEvent_t ev;
+  if (!m->prof_pool.empty()) { ev = m->prof_pool.back(); m->prof_pool.pop_back(); }
+  else { cudaError_t e = cudaEventCreate(&ev); if (e != cudaSuccess) return e; }
+  m->prof_marks.emplace_back(phase, ev);
+  return cudaEventRecord(ev, s);
 }
 
 template <class T>
@@ -282,30 +441,38 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   const int N = b.N, W = c.width, S = c.streams, S1 = m->S1;
   const size_t nsm = ((size_t)W + 40) * 4;
   const int ew = (int)(((size_t)N * W + 255) / 256);
+#define PH(id) CK(mark(m, id, s))
+  PH(DN_SEQ_PH_EMBED);
   CK(launch(k_embed<T>, dim3(N), dim3(128), 0, s, (const T*)m->embed, b, c.embed_scale, W, S1, m->xs));
   for (int li = 0; li < c.n_layers; li++) {
     SeqLayer& l = m->L[li];
     const dn_seq_layer_cfg& lc = l.c;
     auto w = [&](int i) { return (const T*)l.w[i]; };
     // ---- mixer sublayer
+    PH(DN_SEQ_PH_NORM);
     CK(launch(k_read_norm<T>, dim3(N), dim3(128), nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
     T* cst = (T*)m->conv_state + l.conv_off;
-    CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0));
-    if (l.Ck) CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0));
-    if (l.Cv) CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0));
+    auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
+    PH(DN_SEQ_PH_PROJ);
+    CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &m->x_h}));
+    if (l.Ck) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_K), nullptr, &m->x_h}));
+    if (l.Cv) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_h}));
     if (lc.mixer == DN_MIX_ATTENTION) {
       AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, c.eps, l.inv_freq};
       const size_t sm = ((size_t)l.Cq + l.Ck + 40) * 4;
+      PH(DN_SEQ_PH_ATTN_PREP);
       CK(launch(k_attn_prep<T>, dim3(N), dim3(256), sm, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_Q_CONV),
                 w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), w(DN_SQ_Q_NORM), w(DN_SQ_K_NORM), (const T*)cst, m->conv_stride, (T*)m->qb,
                 (T*)m->kpool[l.kv_index], (T*)m->vpool[l.kv_index]));
+      PH(DN_SEQ_PH_ATTN);
       CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(32), (size_t)lc.dim * 4, s, b, (const T*)m->qb, (const T*)m->kpool[l.kv_index],
                 (const T*)m->vpool[l.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, (T*)m->mo));
     } else {
-      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0));
-      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_B], nullptr, m->pb, N, lc.heads, W, true, 0));
-      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0));
+      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));
+      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_B], nullptr, m->pb, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_B), nullptr, &m->x_h}));
+      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0, LinMaps{wm(DN_SQ_G), nullptr, &m->x_h}));
       DeltaPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv};
+      PH(DN_SEQ_PH_DELTA_PREP);
       CK(launch(k_delta_prep<T>, dim3(N), dim3(256), (size_t)2 * l.Cq * 4, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
                 w(DN_SQ_Q_CONV), w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), (const float*)m->pa, (const float*)m->pb, w(DN_SQ_A_LOG),
                 w(DN_SQ_DT_BIAS), (const T*)cst, m->conv_stride, m->qn, m->kn, m->vv, m->beta, m->decay));
@@ -316,32 +483,46 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       float* st = m->delta_state + l.delta_off;
 #define DR(Rv) CK(launch(k_delta_rule<Rv>, grid, dim3(32 * P), 0, s, b, lc.heads, lc.kv_heads, lc.dim, lc.vdim, P, (const float*)m->qn, \
                          (const float*)m->kn, (const float*)m->vv, (const float*)m->beta, (const float*)m->decay, st, m->delta_stride, m->od))
+      PH(DN_SEQ_PH_DELTA_RULE);
       if (R == 8) DR(8); else if (R == 16) DR(16); else DR(32);
 #undef DR
+      PH(DN_SEQ_PH_DELTA_OUT);
       CK(launch(k_delta_out<T>, dim3(N, lc.heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_OUT_NORM), lc.heads, lc.vdim,
                 c.eps, (T*)m->mo));
     }
     if (lc.conv > 1) {
       const int ld = l.Cq + l.Ck + l.Cv;
+      PH(DN_SEQ_PH_CARRY);
       CK(launch(k_conv_carry<T>, dim3((l.Cq + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uq, l.Cq, lc.conv, b, cst, m->conv_stride, ld, 0));
       if (l.Ck) CK(launch(k_conv_carry<T>, dim3((l.Ck + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uk, l.Ck, lc.conv, b, cst, m->conv_stride, ld, l.Cq));
       if (l.Cv) CK(launch(k_conv_carry<T>, dim3((l.Cv + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uv, l.Cv, lc.conv, b, cst, m->conv_stride, ld, l.Cq + l.Ck));
     }
-    CK(linear<T>(s, (const T*)m->mo, l.w[DN_SQ_O], nullptr, m->y, N, W, l.Co, true, 0));
+    PH(DN_SEQ_PH_OUT_PROJ);
+    CK(linear<T>(m, s, (const T*)m->mo, l.w[DN_SQ_O], nullptr, m->y, N, W, l.Co, true, 0, LinMaps{wm(DN_SQ_O), nullptr, &l.x_mo}));
+    PH(DN_SEQ_PH_WRITE_BACK);
     CK(launch(k_write_back<T>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, w(DN_SQ_HC1_MIX), w(DN_SQ_HC1_OUT), (const float*)m->y));
     // ---- feed-forward sublayer
     if (lc.ff > 0) {
+      PH(DN_SEQ_PH_NORM);
       CK(launch(k_read_norm<T>, dim3(N), dim3(128), nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
-      CK(linear<T>(s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, 1));
-      CK(linear<T>(s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0));
+      PH(DN_SEQ_PH_FF_UP);
+      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, 1, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));
+      PH(DN_SEQ_PH_FF_DOWN);
+      CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0, LinMaps{wm(DN_SQ_DOWN), nullptr, &l.x_act}));
+      PH(DN_SEQ_PH_WRITE_BACK);
       CK(launch(k_write_back<T>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, w(DN_SQ_HC2_MIX), w(DN_SQ_HC2_OUT), (const float*)m->y));
     }
+    PH(DN_SEQ_PH_OTHER);
     if (trace) CK(launch(k_stream_sum, dim3(ew), dim3(256), 0, s, (const float*)m->xs, N, W, S1, trace + (size_t)li * N * W));
   }
   if (n_want > 0) {
+    PH(DN_SEQ_PH_NORM);
     CK(launch(k_read_norm<T>, dim3(n_want), dim3(128), nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, 1, 1, c.eps, want_dev, (T*)m->h));
-    CK(linear<T>(s, (const T*)m->h, m->head, nullptr, logits, n_want, c.vocab, W, true, 0));
+    PH(DN_SEQ_PH_HEAD);
+    CK(linear<T>(m, s, (const T*)m->h, m->head, nullptr, logits, n_want, c.vocab, W, true, 0, LinMaps{m->tm_head_ok ? &m->tm_head : nullptr, nullptr, &m->x_h}));
   }
+  PH(DN_SEQ_PH_OTHER);
+#undef PH
   return DN_OK;
 }
 

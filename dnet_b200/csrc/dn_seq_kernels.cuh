@@ -204,6 +204,66 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
   }
 }
 
+// Y[N, O] = X[N, K] W[O, K]^T for a few rows (N <= 8: decode steps): one warp per output feature streams its weight
+// row once (16-byte loads when the row allows) against all N activations; lane partials in ascending k, one
+// shuffle reduction.  The weights are read exactly once: HBM-bound.
+template <class T> struct Vec16 { static constexpr int n = 16 / sizeof(T); };
+template <class T, bool OUT32>
+__global__ void __launch_bounds__(256) k_linear_rows(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
+                                                     void* __restrict__ Y, int N, int O, int K, int act) {
+  constexpr int V = Vec16<T>::n;
+  const int lane = threadIdx.x & 31, o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (o >= O) return;
+  float acc[8], acc2[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = acc2[i] = 0.f;
+  const T* wr = Wt + (size_t)o * K;
+  const T* ur = act ? W2 + (size_t)o * K : nullptr;
+  const bool vec = (K % V == 0) && ((((uintptr_t)Wt | (uintptr_t)X | (uintptr_t)(act ? W2 : Wt)) & 15) == 0);
+  if (vec) {
+    for (int k = lane * V; k < K; k += 32 * V) {
+      T wv[V], uv[V];
+      *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(wr + k);
+      if (act) *reinterpret_cast<uint4*>(uv) = *reinterpret_cast<const uint4*>(ur + k);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        if (i < N) {
+          T xv[V];
+          *reinterpret_cast<uint4*>(xv) = *reinterpret_cast<const uint4*>(X + (size_t)i * K + k);
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            const float x = ldf(xv + j);
+            acc[i] = fmaf(x, ldf(wv + j), acc[i]);
+            if (act) acc2[i] = fmaf(x, ldf(uv + j), acc2[i]);
+          }
+        }
+      }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float w = ldf(wr + k), u = act ? ldf(ur + k) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        if (i < N) {
+          const float x = ldf(X + (size_t)i * K + k);
+          acc[i] = fmaf(x, w, acc[i]);
+          acc2[i] = fmaf(x, u, acc2[i]);
+        }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    if (i < N) {
+      float v = warp_sum(acc[i]);
+      if (act) v = gelu_tanh_f(v) * warp_sum(acc2[i]);
+      if (lane == 0) {
+        if (OUT32) ((float*)Y)[(size_t)i * O + o] = v;
+        else stf((T*)Y + (size_t)i * O + o, v);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // short causal convolution: value of input channel c at `back` steps before row n of its entry
 template <class T>

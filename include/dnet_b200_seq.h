@@ -87,6 +87,21 @@ int dn_seq_free_slots(dn_seq_model* m);
 int dn_seq_step(dn_seq_model* m, int n_entries, const int32_t* slots, const int32_t* counts, const int32_t* tokens_host,
                 int n_want, const int32_t* want_host, float* logits_dev, float* layer_trace_dev, dn_seq_stream s);
 
+/* Synchronises s and reports whether a bounded in-kernel wait ever ran out (negative code; the model's results are
+ * then invalid).  Callers ask before they trust logits they have read. */
+int dn_seq_check(dn_seq_model* m, dn_seq_stream s);
+
+/* Phase profiler (off by default).  While on, every step records an event at each phase boundary; read adds the
+ * elapsed milliseconds of all steps since the last read to per-phase totals and copies them to ms_out
+ * [DN_SEQ_PH_COUNT] (reset != 0 zeroes the totals afterwards).  Synchronises the device. */
+enum {
+  DN_SEQ_PH_EMBED = 0, DN_SEQ_PH_NORM, DN_SEQ_PH_PROJ, DN_SEQ_PH_ATTN_PREP, DN_SEQ_PH_ATTN, DN_SEQ_PH_DELTA_PREP,
+  DN_SEQ_PH_DELTA_RULE, DN_SEQ_PH_DELTA_OUT, DN_SEQ_PH_CARRY, DN_SEQ_PH_OUT_PROJ, DN_SEQ_PH_WRITE_BACK, DN_SEQ_PH_FF_UP,
+  DN_SEQ_PH_FF_DOWN, DN_SEQ_PH_HEAD, DN_SEQ_PH_OTHER, DN_SEQ_PH_COUNT
+};
+int dn_seq_profile(dn_seq_model* m, int on);
+int dn_seq_profile_read(dn_seq_model* m, double* ms_out, int reset);
+
 #ifdef __cplusplus
 }
 #endif

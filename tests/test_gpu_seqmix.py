@@ -327,3 +327,39 @@ def test_greedy_generation_through_the_batcher():
                     assert tok == int(lg.argmax()), r.id
                 seq.append(tok)
             assert len(out[r.id]) == r.max_new_tokens
+
+
+# -- widths whose products run on the tcgen05 GEMM (bf16, 16 tokens and more), the row kernel (a few tokens) and the tiles ----
+WIDE = config([
+    attn(mixer={"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 16, "conv": 3, "rot": {"base": 300.0, "dims": 16}, "mask": {"size": 48}},
+         mlp={"kind": "dense", "ff": 192}),
+    attn(mixer={"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 16, "conv": 3, "rot": {"base": 300.0, "dims": 16}, "mask": {"size": 48},
+                "kv_from": 0}, mlp={"kind": "dense", "ff": 192}),
+    delta(mixer={"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 32, "conv": 4}),
+], streams=2, width=128, vocab=160)
+
+
+def test_tensor_core_products_whole_prompt_and_portions():
+    t = toks(333, seed=120)
+    with Rig(WIDE, "bfloat16") as rig:
+        ref = rig.oracle(t)
+        assert err(run_schedule(rig, t, [333]), ref) < TOL["bfloat16"]
+        # 200 tokens on the GEMM, 12 on the tiles, 5 on the row kernel, 100 on the GEMM, the rest one by one
+        assert err(run_schedule(rig, t, [200, 12, 5, 100]), ref) < TOL["bfloat16"]
+        assert rig.model.check() is None
+
+
+def test_tensor_core_products_in_a_mixed_batch():
+    a, b, c = toks(150, seed=121), toks(40, seed=122), toks(9, seed=123)
+    with Rig(WIDE, "bfloat16") as rig:
+        rig.eng.step([("c", c[:8], [])])
+        lg = rig.eng.step([("a", a, list(range(150))), ("b", b, list(range(40))), ("c", c[8:], [0])])
+        assert err(lg[:150], rig.oracle(a)) < TOL["bfloat16"]
+        assert err(lg[150:190], rig.oracle(b)) < TOL["bfloat16"]
+        assert err(lg[190:], rig.oracle(c)[8:]) < TOL["bfloat16"]
+
+
+def test_wide_model_fp32_is_exact_on_the_cuda_core_path():
+    t = toks(140, seed=124)
+    with Rig(WIDE, "float32") as rig:
+        assert err(run_schedule(rig, t, [100, 3]), rig.oracle(t)) < TOL["float32"]
