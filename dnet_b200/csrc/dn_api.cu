@@ -771,7 +771,7 @@ static cudaError_t gemm_tc(const CUtensorMap& w, const CUtensorMap& w2, const CU
   return launch_tc<32, EPI, (EPI == EPI_SWIGLU ? 5 : 8)>(w, w2, x[0], p, s);
 }
 
-static int layer_forward_tc(dn_model* m, int abs_layer, bf16* x, int T, dn_kv* kv, cudaStream_t s) {
+static int layer_forward_tc(dn_model* m, int abs_layer, bf16* x, int T, dn_kv* kv, cudaStream_t s, cudaEvent_t* ev = nullptr) {
   auto it = m->abs2local.find(abs_layer);
   if (it == m->abs2local.end()) return fail(DN_ENOENT, "Layer %d not hosted on this model instance", abs_layer);
   const int li = it->second;
@@ -784,7 +784,9 @@ static int layer_forward_tc(dn_model* m, int abs_layer, bf16* x, int T, dn_kv* k
   TcParams p;
   memset(&p, 0, sizeof(p));
   p.T = T; p.err = err;
+#define EV(i) do { if (ev) CK(cudaEventRecord(ev[i], s)); } while (0)
 
+  EV(0);
   k_rmsnorm_rows<<<T, 256, 0, s>>>(x, L.w[DN_W_LN1], m->pf_xn, H, c.rms_eps);
   g_launches++;
   p.K = H; p.Y = m->pf_qkv; p.ldy = qkvd;
@@ -800,6 +802,7 @@ static int layer_forward_tc(dn_model* m, int abs_layer, bf16* x, int T, dn_kv* k
                                                                         kvq ? m->kvq_stage_bt : kv->block_table, kv->st, m->inv_freq,
                                                                         c.n_heads, c.n_kv_heads);
   g_launches++;
+  EV(1);
   if (kvq) {
     const int rc = kvq_append_and_attend(m, li, m->pf_q, m->pf_attn, T, kv, s);
     if (rc) return rc;
@@ -820,15 +823,24 @@ static int layer_forward_tc(dn_model* m, int abs_layer, bf16* x, int T, dn_kv* k
 #undef PFA
     g_launches++;
   }
+  EV(2);
   p.K = qd; p.N = H; p.Y = m->pf_h; p.ldy = H; p.col0 = 0; p.resid = x; p.ldr = H;
   CK(gemm_tc<EPI_RESID>(L.tm[3], L.tm[3], m->tm_attn, p, s));
-  if (c.n_experts > 0) return moe_ffn(m, L, m->pf_h, x, T, s);
+  EV(3);
+  if (c.n_experts > 0) {
+    const int rc = moe_ffn(m, L, m->pf_h, x, T, s);
+    if (rc == DN_OK) { EV(4); EV(5); }
+    return rc;
+  }
   k_rmsnorm_rows<<<T, 256, 0, s>>>(m->pf_h, L.w[DN_W_LN2], m->pf_xn, H, c.rms_eps);
   g_launches++;
   p.K = H; p.N = c.ffn; p.Y = m->pf_act; p.ldy = c.ffn; p.resid = nullptr;
   CK(gemm_tc<EPI_SWIGLU>(L.tm[4], L.tm[5], m->tm_xn, p, s));
+  EV(4);
   p.K = c.ffn; p.N = H; p.Y = x; p.ldy = H; p.resid = m->pf_h; p.ldr = H;
   CK(gemm_tc<EPI_RESID>(L.tm[6], L.tm[6], m->tm_act, p, s));
+  EV(5);
+#undef EV
   CK(cudaGetLastError());
   return DN_OK;
 }
@@ -865,7 +877,8 @@ extern "C" int dn_layer_forward_timed(dn_model* m, int abs_layer, void* x_inout,
   for (int i = 0; i < 6; ++i) CK(cudaEventCreate(&ev[i]));
   const int pdl = g_pdl;
   g_pdl = 0;
-  rc = layer_forward(m, abs_layer, (bf16*)x_inout, T, kv, (cudaStream_t)s, ev);
+  rc = T >= 16 ? layer_forward_tc(m, abs_layer, (bf16*)x_inout, T, kv, (cudaStream_t)s, ev)
+               : layer_forward(m, abs_layer, (bf16*)x_inout, T, kv, (cudaStream_t)s, ev);
   g_pdl = pdl;
   if (rc == DN_OK) {
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)s);

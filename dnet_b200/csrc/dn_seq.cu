@@ -425,6 +425,35 @@ static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const voi
   return launch(k_linear<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
 }
 
+// Attention of a step: bf16 steps that bring a prompt portion (an entry of 16 tokens or more) run on the MMA tiles when
+// the head sizes fit its templates; decode-only steps, odd head sizes and fp32 on the one-warp-per-(token, head) kernel.
+template <class T>
+static bool attn_tiles_ok(const dn_seq_layer_cfg& lc, const Batch& b) {
+  return std::is_same<T, bf16>::value && b.max_len >= 16 && lc.dim % 8 == 0 && lc.vdim % 8 == 0 && lc.dim <= 128 && lc.vdim <= 128;
+}
+template <int DKP, int DVP>
+static cudaError_t attn_tiles_launch(cudaStream_t s, const Batch& b, const bf16* q, const bf16* kp, const bf16* vp, const dn_seq_layer_cfg& lc,
+                                     bf16* out) {
+  constexpr size_t smem = ((size_t)2 * AT_ROWS * (DKP + 8) + (size_t)AT_ROWS * (DVP + 8)) * 2;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(k_attn_tiles<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  g_launches++;
+  k_attn_tiles<DKP, DVP><<<dim3(b.row_tiles, lc.heads), 128, smem, s>>>(b, q, kp, vp, lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, out);
+  return cudaGetLastError();
+}
+static cudaError_t attn_tiles(cudaStream_t s, const Batch& b, const bf16* q, const bf16* kp, const bf16* vp, const dn_seq_layer_cfg& lc, bf16* out) {
+  const int kq = lc.dim <= 32 ? 0 : lc.dim <= 64 ? 1 : 2, vq = lc.vdim <= 32 ? 0 : lc.vdim <= 64 ? 1 : 2;
+#define AT(a, c, A, Cc) if (kq == a && vq == c) return attn_tiles_launch<A, Cc>(s, b, q, kp, vp, lc, out);
+  AT(0, 0, 32, 32) AT(0, 1, 32, 64) AT(0, 2, 32, 128) AT(1, 0, 64, 32) AT(1, 1, 64, 64) AT(1, 2, 64, 128)
+  AT(2, 0, 128, 32) AT(2, 1, 128, 64) AT(2, 2, 128, 128)
+#undef AT
+  return cudaErrorInvalidValue;
+}
+
 // phase boundary: the time from this mark to the next one is booked on `phase`
 static cudaError_t mark(dn_seq_model* m, int phase, cudaStream_t s) {
   if (!m->prof_on) return cudaSuccess;
@@ -465,8 +494,11 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
                 w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), w(DN_SQ_Q_NORM), w(DN_SQ_K_NORM), (const T*)cst, m->conv_stride, (T*)m->qb,
                 (T*)m->kpool[l.kv_index], (T*)m->vpool[l.kv_index]));
       PH(DN_SEQ_PH_ATTN);
-      CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(32), (size_t)lc.dim * 4, s, b, (const T*)m->qb, (const T*)m->kpool[l.kv_index],
-                (const T*)m->vpool[l.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, (T*)m->mo));
+      if (attn_tiles_ok<T>(lc, b))
+        CK(attn_tiles(s, b, (const bf16*)m->qb, (const bf16*)m->kpool[l.kv_index], (const bf16*)m->vpool[l.kv_index], lc, (bf16*)m->mo));
+      else
+        CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(32), (size_t)lc.dim * 4, s, b, (const T*)m->qb, (const T*)m->kpool[l.kv_index],
+                  (const T*)m->vpool[l.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, (T*)m->mo));
     } else {
       CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));
       CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_B], nullptr, m->pb, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_B), nullptr, &m->x_h}));
@@ -589,7 +621,9 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
   CK(cudaMemcpyAsync(m->stage_d, h, ints * 4, cudaMemcpyHostToDevice, s));
   CK(cudaEventRecord(m->staged, s));
   int32_t* d = m->stage_d;
-  Batch b{d, d + N, d + 2 * N, d + 3 * N, d + 4 * N, d + 4 * N + E + 1, d + 4 * N + 2 * E + 1, m->bt_d, N, E, m->max_pages};
+  int max_len = 0, row_tiles = 0;
+  for (int e = 0; e < E; e++) { max_len = counts[e] > max_len ? counts[e] : max_len; row_tiles += (counts[e] + AT_ROWS - 1) / AT_ROWS; }
+  Batch b{d, d + N, d + 2 * N, d + 3 * N, d + 4 * N, d + 4 * N + E + 1, d + 4 * N + 2 * E + 1, m->bt_d, N, E, m->max_pages, max_len, row_tiles};
   const int32_t* want_dev = d + 4 * N + 3 * E + 1;
   if (m->cfg.dtype == DN_SEQ_F32) return step_T<float>(m, b, n_want, want_dev, logits, trace, s);
   return step_T<bf16>(m, b, n_want, want_dev, logits, trace, s);

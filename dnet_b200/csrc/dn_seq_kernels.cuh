@@ -77,6 +77,7 @@ struct Batch {
   const int32_t* ent_pos0;   // [E]
   const int32_t* bt;         // [slots][max_pages] page of each 64-token block
   int N, E, max_pages;
+  int max_len, row_tiles;    // longest entry of the step; sum over entries of ceil(tokens / 64)
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -426,6 +427,174 @@ __global__ void __launch_bounds__(32) k_attn(Batch b, const T* __restrict__ q, c
   for (int i = 0; i < 8; i++) {
     const int d = lane + 32 * i;
     if (d < dv) stf(out + ((size_t)n * H + h) * dv + d, acc[i] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same attention for prompt portions, bf16, on the warp-level tensor-core MMA (m16n8k16, fp32 accumulation).
+// A block owns 64 consecutive query rows of one entry and one query head; its four warps take 16 rows each.  Keys
+// and values come page by page (a 64-key tile is exactly one page) through shared memory.  Scores, the running
+// maximum and the running sum are fp32; the weights enter the P V product as a bf16 pair (p = hi + lo, both
+// products accumulated in fp32), which keeps 16 bits of each weight's mantissa.  Per row the key tiles are
+// visited in ascending absolute position and a tile that the row does not see changes nothing, so a row's result
+// does not depend on how the prompt was cut or what else is in the batch.
+// DKP / DVP: head sizes rounded up to the template's; the padding is zero in shared memory.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// rows x cols bf16 from global (row stride ld) into a padded shared tile [64][LDS]; rows >= valid and columns >= cols are zero
+template <int LDS>
+__device__ __forceinline__ void load_tile64(bf16* __restrict__ dst, const bf16* __restrict__ src, size_t ld, int cols, int valid) {
+  const int vec = LDS / 8 - 1;     // 16-byte groups per row, the pad group left out
+  for (int e = threadIdx.x; e < 64 * vec; e += blockDim.x) {
+    const int r = e / vec, c = (e % vec) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid && c < cols) v = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
+    *reinterpret_cast<uint4*>(dst + r * LDS + c) = v;
+  }
+}
+
+constexpr int AT_ROWS = 64;      // query rows of a block, and keys of a tile (= PAGE)
+template <int DKP, int DVP>
+__global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restrict__ q, const bf16* __restrict__ kpool,
+                                                    const bf16* __restrict__ vpool, int H, int G, int dk, int dv, int chunk, float scale,
+                                                    bf16* __restrict__ out) {
+  static_assert(PAGE == AT_ROWS, "a key tile is one page");
+  constexpr int LQ = DKP + 8, LV = DVP + 8;
+  extern __shared__ __align__(16) unsigned char smraw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);
+  bf16* Ks = Qs + AT_ROWS * LQ;
+  bf16* Vs = Ks + AT_ROWS * LQ;
+  // which entry and which of its 64-row tiles
+  int e = 0, t = blockIdx.x;
+  for (; e < b.E; e++) {
+    const int nt = (b.ent_start[e + 1] - b.ent_start[e] + AT_ROWS - 1) / AT_ROWS;
+    if (t < nt) break;
+    t -= nt;
+  }
+  if (e >= b.E) return;
+  const int h = blockIdx.y, g = h / (H / G);
+  const int s0 = b.ent_start[e] + t * AT_ROWS, s1 = b.ent_start[e + 1];
+  const int rows = min(AT_ROWS, s1 - s0);
+  const int p_first = b.ent_pos0[e] + t * AT_ROWS, p_last = p_first + rows - 1;
+  const int Ck = G * dk, Cv = G * dv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  load_tile64<LQ>(Qs, q + ((size_t)s0 * H + h) * dk, (size_t)H * dk, dk, rows);
+  __syncthreads();
+  // this thread's two rows of its warp's 16
+  const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+  const int p0 = r0 < rows ? p_first + r0 : -1, p1 = r1 < rows ? p_first + r1 : -1;
+  const int lo0 = (chunk > 0 && p0 >= 0) ? (p0 / chunk) * chunk : 0, lo1 = (chunk > 0 && p1 >= 0) ? (p1 / chunk) * chunk : 0;
+  const bool warp_live = warp * 16 < rows;
+  uint32_t qf[DKP / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < DKP / 16; kk++) ldsm_x4(qf[kk], Qs + (warp * 16 + (lane & 15)) * LQ + kk * 16 + (lane >> 4) * 8);
+  float o[DVP / 8][4];
+#pragma unroll
+  for (int j = 0; j < DVP / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int32_t* bt = b.bt + (size_t)b.ent_slot[e] * b.max_pages;
+  const int lo_tile = chunk > 0 ? (p_first / chunk) * chunk : 0;
+  for (int j0 = (lo_tile / PAGE) * PAGE; j0 <= p_last; j0 += PAGE) {
+    const size_t prow = (size_t)bt[j0 / PAGE] * PAGE;
+    const int kvalid = min(PAGE, p_last - j0 + 1);      // rows of the page beyond the last query's position are not read
+    __syncthreads();
+    load_tile64<LQ>(Ks, kpool + prow * Ck + (size_t)g * dk, (size_t)Ck, dk, kvalid);
+    load_tile64<LV>(Vs, vpool + prow * Cv + (size_t)g * dv, (size_t)Cv, dv, kvalid);
+    __syncthreads();
+    if (!warp_live) continue;
+    float sc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DKP / 16; kk++) {
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {     // two 8-key tiles per ldmatrix
+        uint32_t kf[4];
+        ldsm_x4(kf, Ks + (jj * 16 + (lane >> 4) * 8 + (lane & 7)) * LQ + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(sc[2 * jj], qf[kk], kf[0], kf[1]);
+        mma_bf16(sc[2 * jj + 1], qf[kk], kf[2], kf[3]);
+      }
+    }
+    // scale, mask, running maximum
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int key = j0 + j * 8 + (lane & 3) * 2 + i;
+        sc[j][i] = (key <= p0 && key >= lo0) ? sc[j][i] * scale : -INFINITY;
+        sc[j][2 + i] = (key <= p1 && key >= lo1) ? sc[j][2 + i] * scale : -INFINITY;
+        mx0 = fmaxf(mx0, sc[j][i]);
+        mx1 = fmaxf(mx1, sc[j][2 + i]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;   // nothing seen yet: weights are 0
+    const float c0 = expf(m0 - u0), c1 = expf(m1 - u1);
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        sc[j][i] = expf(sc[j][i] - u0);
+        sc[j][2 + i] = expf(sc[j][2 + i] - u1);
+        ps0 += sc[j][i];
+        ps1 += sc[j][2 + i];
+      }
+    }
+    ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1); ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
+    ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1); ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
+    l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+    m0 = n0; m1 = n1;
+#pragma unroll
+    for (int j = 0; j < DVP / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+    // O += P V with P = hi + lo
+#pragma unroll
+    for (int kk = 0; kk < 4; kk++) {       // 16 keys per step
+      uint32_t ph[4], pl[4];
+#pragma unroll
+      for (int x = 0; x < 4; x++) {
+        const float a = sc[2 * kk + (x >> 1)][(x & 1) * 2], c = sc[2 * kk + (x >> 1)][(x & 1) * 2 + 1];
+        const float ah = __bfloat162float(__float2bfloat16_rn(a)), ch = __bfloat162float(__float2bfloat16_rn(c));
+        ph[x] = pack_bf16(ah, ch);
+        pl[x] = pack_bf16(a - ah, c - ch);
+      }
+#pragma unroll
+      for (int jj = 0; jj < DVP / 16; jj++) {
+        uint32_t vf[4];
+        ldsm_x4_t(vf, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LV + jj * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * jj], ph, vf[0], vf[1]);
+        mma_bf16(o[2 * jj + 1], ph, vf[2], vf[3]);
+        mma_bf16(o[2 * jj], pl, vf[0], vf[1]);
+        mma_bf16(o[2 * jj + 1], pl, vf[2], vf[3]);
+      }
+    }
+  }
+  if (!warp_live) return;
+  const float i0 = p0 >= 0 ? 1.f / l0 : 0.f, i1 = p1 >= 0 ? 1.f / l1 : 0.f;
+#pragma unroll
+  for (int j = 0; j < DVP / 8; j++) {
+    const int d = j * 8 + (lane & 3) * 2;
+    if (d < dv) {
+      if (p0 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r0) * H + h) * dv + d) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
+      if (p1 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r1) * H + h) * dv + d) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
+    }
   }
 }
 

@@ -359,6 +359,50 @@ def test_tensor_core_products_in_a_mixed_batch():
         assert err(lg[190:], rig.oracle(c)[8:]) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("block", [5, 64, 96, 100])
+def test_block_edges_on_the_attention_tiles(block):
+    """bf16 portions of 16 tokens and more take the MMA-tile attention: the rows at a block's start, whole and cut"""
+    cfg = peaky(config([attn(mixer={"mask": {"size": block}, "conv": 3, "rot": {"base": 30.0, "dims": 8}}, mlp=FF),
+                        attn(mixer={"mask": {"size": block}, "kv_from": 0, "rot": {"base": 30.0, "dims": 8}})], streams=2))
+    n = max(2 * block + 7, 40)
+    t = toks(n, seed=60 + block)
+    edges = [r for r in range(block - 1, n, block)] + [r for r in range(block, n, block)]
+    with Rig(cfg, "bfloat16") as rig:
+        ref = rig.oracle(t)
+        for d in (1, -1):           # a block that is one token longer or shorter moves these rows far beyond the tolerance
+            off = copy.deepcopy(cfg)
+            for L in off["layers"]:
+                L["mixer"]["mask"]["size"] = block + d
+            assert err(so.forward(off, rig.w, t)[[block]], ref[[block]]) > 4 * TOL["bfloat16"]
+        for cuts in ([n], [block + 3, 17, n], [16, 16, 16, n]):
+            got = run_schedule(rig, t, cuts)
+            assert err(got, ref) < TOL["bfloat16"], cuts
+            assert err(got[edges], ref[edges]) < TOL["bfloat16"], cuts
+
+
+def test_far_key_on_the_attention_tiles():
+    """700 keys back, through eleven pages, on the tiles (bf16, whole prompt and 16-token tail portions)"""
+    cfg = config([attn(mixer={"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 16, "scale": 0.5})], vocab=64)
+    w = so.random_weights(cfg, 70)
+    g = torch.Generator().manual_seed(71)
+    e = w["embed"].float()
+    e[63] = -e[62] + 0.4 * torch.randn(e.shape[1], generator=g)
+    w["embed"] = e.to(torch.bfloat16)
+    w["l0.mix.k"] = (-w["l0.mix.q"][:64].float()).to(torch.bfloat16)
+    w["l0.mix.q.norm"] = torch.ones_like(w["l0.mix.q.norm"])
+    w["l0.mix.k.norm"] = torch.ones_like(w["l0.mix.k.norm"])
+    t = torch.randint(0, 62, (700,), generator=g).tolist()
+    t[3] = 63
+    t += [62] * 6
+    with Rig(cfg, "bfloat16", weights=w) as rig:
+        ref = rig.oracle(t)
+        t_without = list(t)
+        t_without[3] = 5
+        assert err(rig.oracle(t_without)[-6:], ref[-6:]) > 4 * TOL["bfloat16"]
+        assert err(run_schedule(rig, t, [len(t)])[-6:], ref[-6:]) < TOL["bfloat16"]
+        assert err(run_schedule(rig, t, [300, 2, 388, 16])[-6:], ref[-6:]) < TOL["bfloat16"]
+
+
 def test_wide_model_fp32_is_exact_on_the_cuda_core_path():
     t = toks(140, seed=124)
     with Rig(WIDE, "float32") as rig:
