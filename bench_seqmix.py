@@ -4,7 +4,7 @@ the llama family at equal width, heads, feed-forward width and depth.  Random we
 
 Per size it reports
   * prefill: one P-token prompt in one step (tokens / second), device time by CUDA events, L2 flushed between steps;
-  * decode: one token per step at a P-token context, for one sequence and for four sequences batched;
+  * decode: one token per step at the end of a P-token context (four sequences: P / 4 tokens each);
   * the device time of every phase of the step (the library's phase timers) next to the llama family's per-kernel
     times (dn_layer_forward_timed), each with its algorithmic FLOPs or bytes and the fraction of the measured peak.
 """
@@ -179,16 +179,21 @@ def llama_algorithmic(cfg: dict, N: int, ctx0: int) -> dict:
     return {"flops": f, "bytes": by}
 
 
-def _roofline(ms: dict, alg: dict, tf_peak: float, gbs_peak: float) -> dict:
-    """Per phase: time, the larger of its tensor-bound and its HBM-bound target time, and target / achieved."""
+FP32_PHASES = ("delta_rule",)      # the recurrence is fp32 FMA on the CUDA cores: its compute bound is the fp32 rate
+
+
+def _roofline(ms: dict, alg: dict, tf_peak: float, gbs_peak: float, f32_tf: float = 0.0) -> dict:
+    """Per phase: time, the larger of its compute-bound and its HBM-bound target time, and target / achieved."""
     out = {}
     for k, t in ms.items():
         if k not in alg["flops"] or t <= 0:
             continue
-        t_f = alg["flops"][k] / (tf_peak * 1e12) * 1e3
+        f32 = k in FP32_PHASES and f32_tf > 0
+        t_f = alg["flops"][k] / ((f32_tf if f32 else tf_peak) * 1e12) * 1e3
         t_b = alg["bytes"][k] / (gbs_peak * 1e9) * 1e3
         tgt = max(t_f, t_b)
-        out[k] = {"ms": round(t, 4), "target_ms": round(tgt, 4), "bound": "tensor" if t_f >= t_b else "hbm", "frac": round(tgt / t, 4)}
+        out[k] = {"ms": round(t, 4), "target_ms": round(tgt, 4), "bound": ("fp32" if f32 else "tensor") if t_f >= t_b else "hbm",
+                  "frac": round(tgt / t, 4)}
     return out
 
 
@@ -224,9 +229,10 @@ def _run_moputar(sz: dict, args, P: int, flush, dev) -> dict:
     model.step([(live[0], prompt)], [P - 1])
     res["prefill"]["phases_ms"] = model.profile_read(reset=True)
     model.profile(False)
-    # decode at a P-token context: 1 sequence, then 4 (contexts P / 4 each so that the pool holds them)
+    # decode at the end of a P-token context: 1 sequence, then 4 with P / 4 tokens each.  The decoded token sits at
+    # the last position of its attention block, so it sees a whole block (or all of the shorter context).
     for n_seq in (1, 4):
-        ctx = P if n_seq == 1 else P // 4
+        ctx = (P if n_seq == 1 else P // 4) - 1
         fresh(n_seq)
         model.step([(h, prompt[:ctx]) for h in live], [])
         toks = [[int(prompt[(i * 7 + 3) % P])] for i in range(n_seq)]
@@ -327,6 +333,8 @@ def run_seqmix(args, rank: int, local_rank: int, world: int) -> None:
     P = int(args.seqmix_prompt)
     gbs, peak_src = B.peaks()
     tf = B.tensor_peak_tf()
+    props = torch.cuda.get_device_properties(dev)
+    f32_tf = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12      # fp32 FMA lanes x 2 x the maximum SM clock
     flush = _Flusher(dev)
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -349,7 +357,7 @@ def run_seqmix(args, rank: int, local_rank: int, world: int) -> None:
                 N, ctx0 = P, 0
             else:
                 N, ctx0 = n_seq, mo[key]["context"]
-            mo[key]["roofline"] = _roofline(mo[key]["phases_ms"], moputar_algorithmic(mcfg, N, ctx0, n_seq), tf, gbs)
+            mo[key]["roofline"] = _roofline(mo[key]["phases_ms"], moputar_algorithmic(mcfg, N, ctx0, n_seq), tf, gbs, f32_tf)
             if key in ll:
                 ll[key]["roofline"] = _roofline(ll[key]["phases_ms"], llama_algorithmic(lcfg, N, ctx0), tf, gbs)
                 mo[key]["vs_llama"] = round(mo[key]["tok_s"] / ll[key]["tok_s"], 4)
@@ -363,7 +371,7 @@ def run_seqmix(args, rank: int, local_rank: int, world: int) -> None:
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
            "config": {"model": "Moputar, random weights", "prompt_len": P, "sizes": args.seqmix_sizes,
                       "timing": "CUDA events around each step, a 256 MB buffer written between steps (L2 flush)",
-                      "peaks": {"bf16_tflops": tf, "hbm_gbs": gbs, "source": peak_src}},
+                      "peaks": {"bf16_tflops": tf, "hbm_gbs": gbs, "source": peak_src, "fp32_tflops_nominal": round(f32_tf, 1)}},
            "gpu_launches": launches, "sizes": sizes, "clocks": sampler.summary(tw0, tw1)}
     sampler.stop()
     B.emit(out)

@@ -5,6 +5,7 @@
 #include "dn_gemm_tc.cuh"      // the tcgen05 / TMA GEMM the llama-family prefill runs on (namespace dn)
 #include "../../include/dnet_b200_seq.h"
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
@@ -469,7 +470,12 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   const dn_seq_cfg& c = m->cfg;
   const int N = b.N, W = c.width, S = c.streams, S1 = m->S1;
   const size_t nsm = ((size_t)W + 40) * 4;
-  const int ew = (int)(((size_t)N * W + 255) / 256);
+  const int ew = (int)(((size_t)N * W + 255) / 256), ew4 = (int)(((size_t)N * W / 4 + 255) / 256);
+  const dim3 nthr(W >= 4096 ? 512 : W >= 2048 ? 256 : 128);     // threads of a norm block: a function of the width only
+  auto write_back = [&](const T* mix, const T* out) {
+    if (W % 4 == 0) return launch(k_write_back<T, 4>, dim3(ew4), dim3(256), 0, s, m->xs, N, W, S, mix, out, (const float*)m->y);
+    return launch(k_write_back<T, 1>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, mix, out, (const float*)m->y);
+  };
 #define PH(id) CK(mark(m, id, s))
   PH(DN_SEQ_PH_EMBED);
   CK(launch(k_embed<T>, dim3(N), dim3(128), 0, s, (const T*)m->embed, b, c.embed_scale, W, S1, m->xs));
@@ -479,13 +485,28 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     auto w = [&](int i) { return (const T*)l.w[i]; };
     // ---- mixer sublayer
     PH(DN_SEQ_PH_NORM);
-    CK(launch(k_read_norm<T>, dim3(N), dim3(128), nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
+    CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
     T* cst = (T*)m->conv_state + l.conv_off;
     auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
     PH(DN_SEQ_PH_PROJ);
-    CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &m->x_h}));
-    if (l.Ck) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_K), nullptr, &m->x_h}));
-    if (l.Cv) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_h}));
+    const bool few = N <= 8;      // a decode step: all projections of the mixer in one launch of the row kernel
+    if (few) {
+      LinSegs sg;
+      memset(&sg, 0, sizeof(sg));
+      auto add = [&](int which, void* y, int rows, int o32) {
+        if (rows <= 0) return;
+        sg.W[sg.n] = l.w[which]; sg.Y[sg.n] = y; sg.O[sg.n] = rows; sg.out32[sg.n] = o32; sg.n++;
+      };
+      add(DN_SQ_Q, m->uq, l.Cq, 0); add(DN_SQ_K, m->uk, l.Ck, 0); add(DN_SQ_V, m->uv, l.Cv, 0);
+      if (lc.mixer == DN_MIX_DELTA) { add(DN_SQ_A, m->pa, lc.heads, 1); add(DN_SQ_B, m->pb, lc.heads, 1); add(DN_SQ_G, m->gt, l.Co, 0); }
+      int blocks = 0;
+      for (int i = 0; i < sg.n; i++) blocks += (sg.O[i] + 7) / 8;
+      CK(launch(k_linear_rows_multi<T>, dim3(blocks), dim3(256), 0, s, (const T*)m->h, sg, N, W));
+    } else {
+      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &m->x_h}));
+      if (l.Ck) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_K), nullptr, &m->x_h}));
+      if (l.Cv) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_h}));
+    }
     if (lc.mixer == DN_MIX_ATTENTION) {
       AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, c.eps, l.inv_freq};
       const size_t sm = ((size_t)l.Cq + l.Ck + 40) * 4;
@@ -497,12 +518,15 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       if (attn_tiles_ok<T>(lc, b))
         CK(attn_tiles(s, b, (const bf16*)m->qb, (const bf16*)m->kpool[l.kv_index], (const bf16*)m->vpool[l.kv_index], lc, (bf16*)m->mo));
       else
-        CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(32), (size_t)lc.dim * 4, s, b, (const T*)m->qb, (const T*)m->kpool[l.kv_index],
+        CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(AT_WARPS * 32), (size_t)(((lc.dim + 3) & ~3) + AT_WARPS * (2 + (lc.vdim + 31) / 32 * 32)) * 4, s, b,
+                  (const T*)m->qb, (const T*)m->kpool[l.kv_index],
                   (const T*)m->vpool[l.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, (T*)m->mo));
     } else {
-      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));
-      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_B], nullptr, m->pb, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_B), nullptr, &m->x_h}));
-      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0, LinMaps{wm(DN_SQ_G), nullptr, &m->x_h}));
+      if (!few) {
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_B], nullptr, m->pb, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_B), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0, LinMaps{wm(DN_SQ_G), nullptr, &m->x_h}));
+      }
       DeltaPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv};
       PH(DN_SEQ_PH_DELTA_PREP);
       CK(launch(k_delta_prep<T>, dim3(N), dim3(256), (size_t)2 * l.Cq * 4, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
@@ -513,7 +537,10 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       if (P > 32) { R = 32; P = 32; }
       dim3 grid(b.E * lc.heads, (lc.vdim + 31) / 32);
       float* st = m->delta_state + l.delta_off;
-#define DR(Rv) CK(launch(k_delta_rule<Rv>, grid, dim3(32 * P), 0, s, b, lc.heads, lc.kv_heads, lc.dim, lc.vdim, P, (const float*)m->qn, \
+      // tokens per staged tile: two tiles of (2 dk + 34) floats each within ~36 KB of shared memory
+      const int per = 2 * lc.dim + 34, TB = std::max(1, std::min(16, 4500 / per));
+      const size_t dsm = (size_t)2 * TB * per * 4;
+#define DR(Rv) CK(launch(k_delta_rule<Rv>, grid, dim3(32 * P), dsm, s, b, lc.heads, lc.kv_heads, lc.dim, lc.vdim, P, TB, (const float*)m->qn, \
                          (const float*)m->kn, (const float*)m->vv, (const float*)m->beta, (const float*)m->decay, st, m->delta_stride, m->od))
       PH(DN_SEQ_PH_DELTA_RULE);
       if (R == 8) DR(8); else if (R == 16) DR(16); else DR(32);
@@ -523,33 +550,31 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
                 c.eps, (T*)m->mo));
     }
     if (lc.conv > 1) {
-      const int ld = l.Cq + l.Ck + l.Cv;
       PH(DN_SEQ_PH_CARRY);
-      CK(launch(k_conv_carry<T>, dim3((l.Cq + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uq, l.Cq, lc.conv, b, cst, m->conv_stride, ld, 0));
-      if (l.Ck) CK(launch(k_conv_carry<T>, dim3((l.Ck + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uk, l.Ck, lc.conv, b, cst, m->conv_stride, ld, l.Cq));
-      if (l.Cv) CK(launch(k_conv_carry<T>, dim3((l.Cv + 127) / 128, b.E), dim3(128), 0, s, (const T*)m->uv, l.Cv, lc.conv, b, cst, m->conv_stride, ld, l.Cq + l.Ck));
+      CarrySrc<T> cs{{(const T*)m->uq, (const T*)m->uk, (const T*)m->uv}, {l.Cq, l.Ck, l.Cv}};
+      CK(launch(k_conv_carry<T>, dim3((std::max(l.Cq, std::max(l.Ck, l.Cv)) + 127) / 128, b.E, 3), dim3(128), 0, s, cs, lc.conv, b, cst, m->conv_stride));
     }
     PH(DN_SEQ_PH_OUT_PROJ);
     CK(linear<T>(m, s, (const T*)m->mo, l.w[DN_SQ_O], nullptr, m->y, N, W, l.Co, true, 0, LinMaps{wm(DN_SQ_O), nullptr, &l.x_mo}));
     PH(DN_SEQ_PH_WRITE_BACK);
-    CK(launch(k_write_back<T>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, w(DN_SQ_HC1_MIX), w(DN_SQ_HC1_OUT), (const float*)m->y));
+    CK(write_back(w(DN_SQ_HC1_MIX), w(DN_SQ_HC1_OUT)));
     // ---- feed-forward sublayer
     if (lc.ff > 0) {
       PH(DN_SEQ_PH_NORM);
-      CK(launch(k_read_norm<T>, dim3(N), dim3(128), nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
+      CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
       PH(DN_SEQ_PH_FF_UP);
       CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, 1, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));
       PH(DN_SEQ_PH_FF_DOWN);
       CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0, LinMaps{wm(DN_SQ_DOWN), nullptr, &l.x_act}));
       PH(DN_SEQ_PH_WRITE_BACK);
-      CK(launch(k_write_back<T>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, w(DN_SQ_HC2_MIX), w(DN_SQ_HC2_OUT), (const float*)m->y));
+      CK(write_back(w(DN_SQ_HC2_MIX), w(DN_SQ_HC2_OUT)));
     }
     PH(DN_SEQ_PH_OTHER);
     if (trace) CK(launch(k_stream_sum, dim3(ew), dim3(256), 0, s, (const float*)m->xs, N, W, S1, trace + (size_t)li * N * W));
   }
   if (n_want > 0) {
     PH(DN_SEQ_PH_NORM);
-    CK(launch(k_read_norm<T>, dim3(n_want), dim3(128), nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, 1, 1, c.eps, want_dev, (T*)m->h));
+    CK(launch(k_read_norm<T>, dim3(n_want), nthr, nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, 1, 1, c.eps, want_dev, (T*)m->h));
     PH(DN_SEQ_PH_HEAD);
     CK(linear<T>(m, s, (const T*)m->h, m->head, nullptr, logits, n_want, c.vocab, W, true, 0, LinMaps{m->tm_head_ok ? &m->tm_head : nullptr, nullptr, &m->x_h}));
   }

@@ -92,11 +92,13 @@ __global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W
   }
 }
 
-// stream read-out (u = sum_s in[s] x_s, or x_0) + RMS norm with weight (1 + w) or w; rows[] optionally gathers
+// stream read-out (u = sum_s in[s] x_s, or x_0) + RMS norm with weight (1 + w) or w; rows[] optionally gathers.
+// 16-byte loads of the streams when the width allows; a thread's partial sum of squares runs over its own columns in
+// ascending order and the block adds the partials by index, so the result depends on W and the block size only.
 template <class T>
 __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, const T* __restrict__ hc_in, const T* __restrict__ nw,
                             int one_plus, int sum_all, float eps, const int32_t* __restrict__ rows, T* __restrict__ h) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* u = sm;            // [W]
   float* red = sm + W;      // [33]
   const int r = blockIdx.x, n = rows ? rows[r] : r;
@@ -104,11 +106,23 @@ __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, c
   const int S1 = S > 0 ? S : 1;
   for (int s = 0; s < S1; s++) cin[s] = (S > 0 && !sum_all) ? ldf(hc_in + s) : 1.f;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < S1; s++) a += cin[s] * xs[((size_t)s * N + n) * W + c];
-    u[c] = a;
-    ss += a * a;
+  if ((W & 3) == 0) {
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < S1; s++) {
+        const float4 x = *reinterpret_cast<const float4*>(xs + ((size_t)s * N + n) * W + c);
+        a.x += cin[s] * x.x; a.y += cin[s] * x.y; a.z += cin[s] * x.z; a.w += cin[s] * x.w;
+      }
+      *reinterpret_cast<float4*>(u + c) = a;
+      ss += a.x * a.x; ss += a.y * a.y; ss += a.z * a.z; ss += a.w * a.w;
+    }
+  } else {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      float a = 0.f;
+      for (int s = 0; s < S1; s++) a += cin[s] * xs[((size_t)s * N + n) * W + c];
+      u[c] = a;
+      ss += a * a;
+    }
   }
   ss = block_sum(ss, red);
   const float rinv = 1.f / sqrtf(ss / (float)W + eps);
@@ -118,20 +132,51 @@ __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, c
   }
 }
 
-// stream write-back: x_t <- sum_s mix[s][t] x_s + out[t] y   (S = 0: x <- x + y)
-template <class T>
+// stream write-back: x_t <- sum_s mix[s][t] x_s + out[t] y   (S = 0: x <- x + y); VEC elements per thread
+template <class T, int VEC>
 __global__ void k_write_back(float* __restrict__ xs, int N, int W, int S, const T* __restrict__ mix, const T* __restrict__ out,
                              const float* __restrict__ y) {
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)N * W) return;
-  if (S <= 0) { xs[i] += y[i]; return; }
-  float x[MAX_STREAMS];
-  for (int s = 0; s < S; s++) x[s] = xs[(size_t)s * N * W + i];
-  const float yy = y[i];
+  __shared__ float cm[MAX_STREAMS * MAX_STREAMS + MAX_STREAMS];
+  for (int i = threadIdx.x; i < S * S + S; i += blockDim.x) cm[i] = i < S * S ? ldf(mix + i) : ldf(out + (i - S * S));
+  __syncthreads();
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC, NW = (size_t)N * W;
+  if (i >= NW) return;
+  float yy[VEC], x[MAX_STREAMS][VEC];
+  if (VEC == 4) *reinterpret_cast<float4*>(yy) = *reinterpret_cast<const float4*>(y + i);
+  else yy[0] = y[i];
+  if (S <= 0) {
+    float* xp = xs + i;
+    if (VEC == 4) {
+      float4 v = *reinterpret_cast<float4*>(xp);
+      v.x += yy[0]; v.y += yy[1]; v.z += yy[2]; v.w += yy[3];
+      *reinterpret_cast<float4*>(xp) = v;
+    } else xp[0] += yy[0];
+    return;
+  }
+#pragma unroll
+  for (int s = 0; s < MAX_STREAMS; s++) {
+    if (s < S) {
+      if (VEC == 4) *reinterpret_cast<float4*>(x[s]) = *reinterpret_cast<const float4*>(xs + (size_t)s * NW + i);
+      else x[s][0] = xs[(size_t)s * NW + i];
+    }
+  }
   for (int t = 0; t < S; t++) {
-    float a = 0.f;
-    for (int s = 0; s < S; s++) a += ldf(mix + s * S + t) * x[s];
-    xs[(size_t)t * N * W + i] = a + ldf(out + t) * yy;
+    float a[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) a[v] = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; s++) {
+      if (s < S) {
+        const float m = cm[s * S + t];
+#pragma unroll
+        for (int v = 0; v < VEC; v++) a[v] += m * x[s][v];
+      }
+    }
+    const float ot = cm[S * S + t];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) a[v] += ot * yy[v];
+    if (VEC == 4) *reinterpret_cast<float4*>(xs + (size_t)t * NW + i) = *reinterpret_cast<float4*>(a);
+    else xs[(size_t)t * NW + i] = a[0];
   }
 }
 
@@ -209,12 +254,12 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
 // row once (16-byte loads when the row allows) against all N activations; lane partials in ascending k, one
 // shuffle reduction.  The weights are read exactly once: HBM-bound.
 template <class T> struct Vec16 { static constexpr int n = 16 / sizeof(T); };
-template <class T, bool OUT32>
-__global__ void __launch_bounds__(256) k_linear_rows(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
-                                                     void* __restrict__ Y, int N, int O, int K, int act) {
+// one warp, one output feature o of one product
+template <class T>
+__device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2, void* __restrict__ Y,
+                                           bool out32, int N, int O, int K, int act, int o) {
   constexpr int V = Vec16<T>::n;
-  const int lane = threadIdx.x & 31, o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (o >= O) return;
+  const int lane = threadIdx.x & 31;
   float acc[8], acc2[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = acc2[i] = 0.f;
@@ -258,11 +303,41 @@ __global__ void __launch_bounds__(256) k_linear_rows(const T* __restrict__ X, co
       float v = warp_sum(acc[i]);
       if (act) v = gelu_tanh_f(v) * warp_sum(acc2[i]);
       if (lane == 0) {
-        if (OUT32) ((float*)Y)[(size_t)i * O + o] = v;
+        if (out32) ((float*)Y)[(size_t)i * O + o] = v;
         else stf((T*)Y + (size_t)i * O + o, v);
       }
     }
   }
+}
+template <class T, bool OUT32>
+__global__ void __launch_bounds__(256) k_linear_rows(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
+                                                     void* __restrict__ Y, int N, int O, int K, int act) {
+  const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (o >= O) return;
+  linear_row<T>(X, Wt, W2, Y, OUT32, N, O, K, act, o);
+}
+// several products of the same few rows in one launch (the projections of a mixer in a decode step): blocks are
+// dealt to the products in order, 8 output features each
+constexpr int MAX_SEGS = 6;
+struct LinSegs {
+  const void* W[MAX_SEGS];
+  void* Y[MAX_SEGS];
+  int O[MAX_SEGS];
+  int out32[MAX_SEGS];
+  int n;
+};
+template <class T>
+__global__ void __launch_bounds__(256) k_linear_rows_multi(const T* __restrict__ X, LinSegs sg, int N, int K) {
+  int blk = blockIdx.x, i = 0;
+  for (; i < sg.n; i++) {
+    const int nb = (sg.O[i] + 7) / 8;
+    if (blk < nb) break;
+    blk -= nb;
+  }
+  if (i >= sg.n) return;
+  const int o = blk * 8 + (threadIdx.x >> 5);
+  if (o >= sg.O[i]) return;
+  linear_row<T>(X, (const T*)sg.W[i], (const T*)nullptr, sg.Y[i], sg.out32[i] != 0, N, sg.O[i], K, 0, o);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -282,12 +357,17 @@ __device__ __forceinline__ float conv_at(const T* __restrict__ U, int ldu, const
   return a;
 }
 
-// after a step: the last taps-1 inputs of every entry become its slot's carried inputs
+// after a step: the last taps-1 inputs of every entry become its slot's carried inputs; blockIdx.z picks the
+// projection (q, k, v; a width of 0 means the layer has none of its own)
 template <class T>
-__global__ void k_conv_carry(const T* __restrict__ U, int C, int taps, Batch b, T* __restrict__ state, size_t slot_stride, int ldst,
-                             int coff) {
+struct CarrySrc { const T* U[3]; int C[3]; };
+template <class T>
+__global__ void k_conv_carry(CarrySrc<T> src, int taps, Batch b, T* __restrict__ state, size_t slot_stride) {
+  const int z = blockIdx.z, C = src.C[z];
   const int e = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
+  const T* U = src.U[z];
+  const int ldst = src.C[0] + src.C[1] + src.C[2], coff = z == 0 ? 0 : z == 1 ? src.C[0] : src.C[0] + src.C[1];
   const int s0 = b.ent_start[e], len = b.ent_start[e + 1] - s0;
   T* st = state + (size_t)b.ent_slot[e] * slot_stride + coff;
   T keep[8];
@@ -378,33 +458,76 @@ __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const
 }
 
 // paged attention of one (token, head): keys lo..p with lo the start of the query's block of `chunk` positions
-// (0: the sequence's start); fp32 scores, online softmax over 32-key tiles, fixed order.  One warp per block.
+// (0: the sequence's start); fp32 scores and weights.  One block per (token, head); its AT_WARPS warps take the
+// 32-key tiles (counted from lo) round-robin, each with its own running maximum, sum and output, and the block
+// merges the warps' partials in warp order -- a row's result depends on its own position only.  A lane scores
+// one key of the tile (its K row in 16-byte loads when the head size allows) and owns ceil(dv / 32) adjacent
+// output dims.
+constexpr int AT_WARPS = 8;
 template <class T>
-__global__ void __launch_bounds__(32) k_attn(Batch b, const T* __restrict__ q, const T* __restrict__ kpool, const T* __restrict__ vpool,
-                                             int H, int G, int dk, int dv, int chunk, float scale, T* __restrict__ out) {
-  extern __shared__ float sm[];
-  float* qs = sm;   // [dk]
-  const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+__device__ __forceinline__ void ld_vals(float (&v)[8], const T* p, int cnt, bool vec) {
+  if (vec) {
+    const int bytes = cnt * (int)sizeof(T);
+    if (bytes == 16) {
+      uint4 raw = *reinterpret_cast<const uint4*>(p);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 16 / (int)sizeof(T); i++) v[i] = ldf(e + i);
+      return;
+    }
+    if (bytes == 8) {
+      uint2 raw = *reinterpret_cast<const uint2*>(p);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8 / (int)sizeof(T); i++) v[i] = ldf(e + i);
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) if (i < cnt) v[i] = ldf(p + i);
+}
+template <class T>
+__global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __restrict__ q, const T* __restrict__ kpool,
+                                                        const T* __restrict__ vpool, int H, int G, int dk, int dv, int chunk, float scale,
+                                                        T* __restrict__ out) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int V = 16 / (int)sizeof(T);
+  const int VPL = (dv + 31) / 32, dvp = VPL * 32;
+  float* qs = sm;                                   // [dk rounded up to 4]
+  float* part = sm + ((dk + 3) & ~3);               // [AT_WARPS][2 + dvp]
+  const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = h / (H / G), slot = b.slot[n], p = b.pos[n];
   const int lo = chunk > 0 ? (p / chunk) * chunk : 0;
   const int Ck = G * dk, Cv = G * dv;
-  for (int d = lane; d < dk; d += 32) qs[d] = ldf(q + ((size_t)n * H + h) * dk + d);
-  __syncwarp();
+  for (int d = threadIdx.x; d < dk; d += blockDim.x) qs[d] = ldf(q + ((size_t)n * H + h) * dk + d);
+  __syncthreads();
   const int32_t* bt = b.bt + (size_t)slot * b.max_pages;
+  const bool kvec = (dk % V) == 0;                  // K rows start on 16-byte boundaries
+  const int vcnt = min(VPL, max(0, dv - lane * VPL));
+  const bool vvec = (dv % 32) == 0;
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.f;
-  for (int j0 = lo; j0 <= p; j0 += 32) {
+  for (int j0 = lo + warp * 32; j0 <= p; j0 += AT_WARPS * 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
     if (j <= p) {
       const T* kr = kpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Ck + g * dk;
       float d0 = 0.f;
-      for (int d = 0; d < dk; d++) d0 = fmaf(qs[d], ldf(kr + d), d0);
+      if (kvec) {
+        for (int d = 0; d < dk; d += V) {
+          uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
+          const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int x = 0; x < V; x++) d0 = fmaf(qs[d + x], ldf(e + x), d0);
+        }
+      } else {
+        for (int d = 0; d < dk; d++) d0 = fmaf(qs[d], ldf(kr + d), d0);
+      }
       s = d0 * scale;
     }
     const float mn = fmaxf(m, warp_max(s));
-    const float corr = expf(m - mn);      // exp(-inf) = 0 on the first tile
+    const float corr = expf(m - mn);      // exp(-inf) = 0 on the warp's first tile
     const float pj = j <= p ? expf(s - mn) : 0.f;
     l = l * corr + warp_sum(pj);
 #pragma unroll
@@ -413,20 +536,32 @@ __global__ void __launch_bounds__(32) k_attn(Batch b, const T* __restrict__ q, c
     for (int t = 0; t < cnt; t++) {
       const float pt = __shfl_sync(0xffffffffu, pj, t);
       const int jj = j0 + t;
-      const T* vr = vpool + ((size_t)bt[jj / PAGE] * PAGE + (jj % PAGE)) * Cv + g * dv;
+      const T* vr = vpool + ((size_t)bt[jj / PAGE] * PAGE + (jj % PAGE)) * Cv + g * dv + lane * VPL;
+      float vv[8];
+      ld_vals(vv, vr, vcnt, vvec);
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int d = lane + 32 * i;
-        if (d < dv) acc[i] = fmaf(pt, ldf(vr + d), acc[i]);
-      }
+      for (int i = 0; i < 8; i++)
+        if (i < vcnt) acc[i] = fmaf(pt, vv[i], acc[i]);
     }
     m = mn;
   }
-  const float inv = 1.f / l;
+  float* mine = part + (size_t)warp * (2 + dvp);
+  if (lane == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const int d = lane + 32 * i;
-    if (d < dv) stf(out + ((size_t)n * H + h) * dv + d, acc[i] * inv);
+  for (int i = 0; i < 8; i++)
+    if (i < VPL) mine[2 + lane * VPL + i] = acc[i];
+  __syncthreads();
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float M = -INFINITY;
+    for (int w = 0; w < AT_WARPS; w++) M = fmaxf(M, part[(size_t)w * (2 + dvp)]);
+    float L = 0.f, a = 0.f;
+    for (int w = 0; w < AT_WARPS; w++) {
+      const float* pw = part + (size_t)w * (2 + dvp);
+      const float f = expf(pw[0] - M);     // a warp that saw no tile has maximum -inf and weight 0
+      L += pw[1] * f;
+      a += pw[2 + d] * f;
+    }
+    stf(out + ((size_t)n * H + h) * dv + d, a / L);
   }
 }
 
@@ -645,48 +780,85 @@ __global__ void k_delta_prep(DeltaPrep a, Batch b, const T* __restrict__ Uq, con
 
 // The recurrence, token by token:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
 // Columns of S are independent: a block owns 32 columns of one (entry, head); P adjacent lanes share a column,
-// each holding R = ceil(dk / P) of its rows in registers.  State [slot][head][dk][dv] fp32.
+// each holding R = ceil(dk / P) of its rows (rows part, part + P, ...) in registers.  State [slot][head][dk][dv] fp32.
+// The tokens' inputs (k, q, the block's 32 values, decay, beta) come through shared memory in tiles of TB tokens,
+// copied asynchronously one tile ahead, so that the serial chain of a token is registers, shared memory and the
+// lane shuffles only.  Sums run in an order fixed by (dk, P): four interleaved partial sums over a thread's rows,
+// then the lanes of a column pairwise -- nothing depends on the tile size or on where a portion was cut.
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
 template <int R>
-__global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, const float* __restrict__ qn, const float* __restrict__ kn,
+__global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int TB, const float* __restrict__ qn, const float* __restrict__ kn,
                              const float* __restrict__ vv, const float* __restrict__ beta, const float* __restrict__ decay,
                              float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+  extern __shared__ __align__(16) float dsm[];      // 2 x TB x per
+  const int per = 2 * dk + 34;                      // k[dk] q[dk] v[32] decay beta
   const int e = blockIdx.x / H, h = blockIdx.x % H, g = h / (H / G);
-  const int part = threadIdx.x % P, col = blockIdx.y * 32 + threadIdx.x / P;
+  const int part = threadIdx.x % P, colb = threadIdx.x / P, col = blockIdx.y * 32 + colb;
   const int s0 = b.ent_start[e], s1 = b.ent_start[e + 1];
   const bool live = col < dv;
   float* Sg = state + (size_t)b.ent_slot[e] * slot_stride + (size_t)h * dk * dv;
-  const int r0 = part * R;
   float S[R];
 #pragma unroll
-  for (int r = 0; r < R; r++) S[r] = (live && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col] : 0.f;
+  for (int r = 0; r < R; r++) S[r] = (live && r * P + part < dk) ? Sg[(size_t)(r * P + part) * dv + col] : 0.f;
   const int Cq = G * dk, Cv = H * dv;
-  for (int n = s0; n < s1; n++) {
-    const float* kr = kn + (size_t)n * Cq + g * dk + r0;
-    const float* qr = qn + (size_t)n * Cq + g * dk + r0;
-    const float gd = decay[(size_t)n * H + h], bt = beta[(size_t)n * H + h];
-    const float v = live ? vv[(size_t)n * Cv + h * dv + col] : 0.f;
-    float kk[R];
-    float dot = 0.f;
-#pragma unroll
-    for (int r = 0; r < R; r++) {
-      kk[r] = r0 + r < dk ? kr[r] : 0.f;
-      S[r] *= gd;
-      dot = fmaf(S[r], kk[r], dot);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  auto stage = [&](int buf, int n0) {
+    const int cnt = min(TB, s1 - n0);
+    for (int t = warp; t < cnt; t += nwarp) {
+      const int n = n0 + t;
+      float* dst = dsm + ((size_t)buf * TB + t) * per;
+      const float* kr = kn + (size_t)n * Cq + g * dk;
+      const float* qr = qn + (size_t)n * Cq + g * dk;
+      for (int c = lane; c < dk; c += 32) { cp_async4(dst + c, kr + c); cp_async4(dst + dk + c, qr + c); }
+      const int vc = blockIdx.y * 32 + lane;
+      if (vc < dv) cp_async4(dst + 2 * dk + lane, vv + (size_t)n * Cv + h * dv + vc);
+      else dst[2 * dk + lane] = 0.f;
+      if (lane == 0) cp_async4(dst + 2 * dk + 32, decay + (size_t)n * H + h);
+      if (lane == 1) cp_async4(dst + 2 * dk + 33, beta + (size_t)n * H + h);
     }
-    for (int x = 1; x < P; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
-    const float u = bt * (v - dot);
-    float od = 0.f;
+    cp_async_commit();
+  };
+  stage(0, s0);
+  int buf = 0;
+  for (int n0 = s0; n0 < s1; n0 += TB, buf ^= 1) {
+    if (n0 + TB < s1) { stage(buf ^ 1, n0 + TB); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();
+    const int cnt = min(TB, s1 - n0);
+    for (int t = 0; t < cnt; t++) {
+      const float* in = dsm + ((size_t)buf * TB + t) * per;
+      const float gd = in[2 * dk + 32], bt = in[2 * dk + 33], v = in[2 * dk + colb];
+      float kk[R], d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-      S[r] = fmaf(kk[r], u, S[r]);
-      od = fmaf(S[r], r0 + r < dk ? qr[r] : 0.f, od);
+      for (int r = 0; r < R; r++) {
+        kk[r] = r * P + part < dk ? in[r * P + part] : 0.f;
+        S[r] *= gd;
+        d4[r & 3] = fmaf(S[r], kk[r], d4[r & 3]);
+      }
+      float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      for (int x = 1; x < P; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+      const float u = bt * (v - dot);
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        S[r] = fmaf(kk[r], u, S[r]);
+        o4[r & 3] = fmaf(S[r], r * P + part < dk ? in[dk + r * P + part] : 0.f, o4[r & 3]);
+      }
+      float od = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+      for (int x = 1; x < P; x <<= 1) od += __shfl_xor_sync(0xffffffffu, od, x);
+      if (live && part == 0) o[(size_t)(n0 + t) * Cv + h * dv + col] = od;
     }
-    for (int x = 1; x < P; x <<= 1) od += __shfl_xor_sync(0xffffffffu, od, x);
-    if (live && part == 0) o[(size_t)n * Cv + h * dv + col] = od;
+    __syncthreads();      // the tile is read out before the copy after next lands in it
   }
 #pragma unroll
   for (int r = 0; r < R; r++)
-    if (live && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col] = S[r];
+    if (live && r * P + part < dk) Sg[(size_t)(r * P + part) * dv + col] = S[r];
 }
 
 // read-out of the recurrence: per head o / rms(o) * w * silu(gate) -> T.  One warp per (token, head).

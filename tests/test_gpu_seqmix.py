@@ -407,3 +407,67 @@ def test_wide_model_fp32_is_exact_on_the_cuda_core_path():
     t = toks(140, seed=124)
     with Rig(WIDE, "float32") as rig:
         assert err(run_schedule(rig, t, [100, 3]), rig.oracle(t)) < TOL["float32"]
+
+
+# -- from a checkpoint folder, through the command lines --------------------------------------------------------------
+def write_checkpoint(folder, cfg, weights):
+    """config.json + model.safetensors (bf16 tensors), written by hand: header length, JSON header, data"""
+    import json
+    import struct
+
+    header, blobs, at = {}, [], 0
+    for name, t in weights.items():
+        raw = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(folder / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+    (folder / "config.json").write_text(json.dumps(cfg))
+
+
+def test_command_lines_on_a_checkpoint_folder(tmp_path):
+    import json
+    import pathlib
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    root = pathlib.Path(__file__).resolve().parent.parent
+    w = so.random_weights(FULL, 9)
+    write_checkpoint(tmp_path, FULL, w)
+    a, b = toks(70, seed=130), toks(21, seed=131)
+    # replay: a's prompt in two portions beside b, then a decoded token of each; the cache holds 3 pages
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": []}, {"id": "b", "tokens": b[:20], "want": [19]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[40:69], "want": [0, 28]}, {"id": "b", "tokens": b[20:], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == ["done 0", "done 1", "done 2"]
+    ra, rb = so.forward(FULL, w, a), so.forward(FULL, w, b)
+    V = FULL["vocab"]
+    got = {i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)) for i in range(3)}
+    assert err(got[0], rb[[19]]) < TOL["float32"]
+    assert err(got[1], torch.stack([ra[40], ra[68], rb[20]])) < TOL["float32"]
+    assert err(got[2], ra[[69]]) < TOL["float32"]
+    # generation: greedy tokens of two requests equal the oracle's (ties aside)
+    reqs = [{"id": "x", "prompt": a[:30], "max_new_tokens": 4}, {"id": "y", "prompt": b[:5]}]
+    r = subprocess.run([sys.executable, str(root / "bin" / "generate"), "--model", str(tmp_path), "--dtype", "float32", "--max-new-tokens", "3",
+                        "--max-tokens", "128", "--max-seqs", "2"], input="".join(json.dumps(q) + "\n" for q in reqs), capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    res = {o["id"]: o["tokens"] for o in map(json.loads, r.stdout.strip().splitlines())}
+    assert len(res["x"]) == 4 and len(res["y"]) == 3
+    for q in reqs:
+        seq = list(q["prompt"])
+        for tok in res[q["id"]]:
+            lg = so.forward(FULL, w, seq)[-1]
+            top = torch.topk(lg, 2).values
+            if float(top[0] - top[1]) > 1e-3 * float(lg.std()):
+                assert tok == int(lg.argmax())
+            seq.append(tok)
