@@ -212,21 +212,22 @@ def _run_moputar(sz: dict, args, P: int, flush, dev) -> dict:
     prompt = torch.randint(0, VOCAB, (P,), generator=torch.Generator().manual_seed(11)).tolist()
     K, Wm = args.steps, args.warmup
     live = []
+    st = torch.cuda.current_stream()      # run_seqmix made a side stream current: decode steps replay graphs there
 
     def fresh(n):
         for h in live:
             h.free()
         live.clear()
-        live.extend(model.make_cache() for _ in range(n))
+        live.extend(model.make_cache(stream=st) for _ in range(n))
 
     res = {"config": {"layers": [l["type"] + ("<-%d" % l["mixer"]["kv_from"] if "kv_from" in l["mixer"] else "") for l in cfg["layers"]],
                       "streams": cfg["streams"], "chunk": args.seqmix_chunk, "conv": 4, "rot_dims": 64}}
     # prefill: one P-token entry, logits of the last token
-    t = _timed(lambda: model.step([(live[0], prompt)], [P - 1]), lambda: fresh(1), K, Wm, flush)
+    t = _timed(lambda: model.step([(live[0], prompt)], [P - 1], stream=st), lambda: fresh(1), K, Wm, flush)
     res["prefill"] = {"ms": t, "tok_s": P / t * 1e3}
     fresh(1)
     model.profile(True)
-    model.step([(live[0], prompt)], [P - 1])
+    model.step([(live[0], prompt)], [P - 1], stream=st)
     res["prefill"]["phases_ms"] = model.profile_read(reset=True)
     model.profile(False)
     # decode at the end of a P-token context: 1 sequence, then 4 with P / 4 tokens each.  The decoded token sits at
@@ -234,20 +235,20 @@ def _run_moputar(sz: dict, args, P: int, flush, dev) -> dict:
     for n_seq in (1, 4):
         ctx = (P if n_seq == 1 else P // 4) - 1
         fresh(n_seq)
-        model.step([(h, prompt[:ctx]) for h in live], [])
+        model.step([(h, prompt[:ctx]) for h in live], [], stream=st)
         toks = [[int(prompt[(i * 7 + 3) % P])] for i in range(n_seq)]
         want = list(range(n_seq))
-        t = _timed(lambda: model.step([(h, toks[i]) for i, h in enumerate(live)], want), lambda: None, K, Wm, flush)
+        t = _timed(lambda: model.step([(h, toks[i]) for i, h in enumerate(live)], want, stream=st), lambda: None, K, Wm, flush)
         key = "decode_bs%d" % n_seq
         res[key] = {"ms": t, "tok_s": n_seq / t * 1e3, "context": ctx}
         model.profile(True)
         for _ in range(4):
             flush()
-            model.step([(h, toks[i]) for i, h in enumerate(live)], want)
+            model.step([(h, toks[i]) for i, h in enumerate(live)], want, stream=st)
         ph = model.profile_read(reset=True)
         model.profile(False)
         res[key]["phases_ms"] = {k: v / 4 for k, v in ph.items()}
-    model.check()
+    model.check(st)
     fresh(0)
     launches = int(model._lib.dn_seq_launch_count())
     model.destroy()
@@ -336,6 +337,7 @@ def run_seqmix(args, rank: int, local_rank: int, world: int) -> None:
     props = torch.cuda.get_device_properties(dev)
     f32_tf = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12      # fp32 FMA lanes x 2 x the maximum SM clock
     flush = _Flusher(dev)
+    side = torch.cuda.Stream(device=dev)
     sampler = ClockSampler(local_rank)
     sampler.start()
     import time
@@ -345,7 +347,9 @@ def run_seqmix(args, rank: int, local_rank: int, world: int) -> None:
     launches = 0
     for name in args.seqmix_sizes.split(","):
         sz = SIZES[name]
-        mo = _run_moputar(sz, args, P, flush, dev)
+        with torch.cuda.stream(side):
+            mo = _run_moputar(sz, args, P, flush, dev)
+        side.synchronize()
         log(f"{name}: moputar prefill {mo['prefill']['ms']:.2f} ms, phases " + ", ".join(f"{k} {v:.2f}" for k, v in mo["prefill"]["phases_ms"].items() if v > 0))
         log(f"{name}: moputar decode bs1 {mo['decode_bs1']['ms']:.3f} ms, phases " + ", ".join(f"{k} {v:.3f}" for k, v in mo["decode_bs1"]["phases_ms"].items() if v > 0))
         ll = _run_llama(sz, args, P, len(mo["cfg"]["layers"]), flush, dev)

@@ -60,6 +60,7 @@ _PROTOS = {
     "dn_seq_check": (_i, [_vp, _vp]),
     "dn_seq_profile": (_i, [_vp, _i]),
     "dn_seq_profile_read": (_i, [_vp, C.POINTER(C.c_double), _i]),
+    "dn_seq_set_graphs": (_i, [_vp, _i]),
     "dn_seq_step": (_i, [_vp, _i, _I32P, _I32P, _I32P, _i, _I32P, _vp, _vp, _vp]),
 }
 _lib = None

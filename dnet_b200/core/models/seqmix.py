@@ -90,7 +90,7 @@ class SeqMixRingModel(BaseRingModel):
 
     model_type: Optional[str] = None
     step_kernel_ok = False
-    batched_step = True        # the runtime drives this family through shard.batching.SequenceBatcher
+    batched_step = True        # served by shard.batching.SequenceBatcher (step function + token loop), not by the ring policies
 
     def __init__(self, model_config: Any, assigned_layers: Optional[List[int]] = None, is_api_layer: bool = False, *,
                  dtype: str = "bfloat16", kv_pool_pages: int = 0, max_seqs: int = 4, max_batch_tokens: int = 2048, **_ignored):
@@ -237,6 +237,10 @@ class SeqMixRingModel(BaseRingModel):
     def profile(self, on: bool) -> None:
         """Switch the per-phase device timers of the step on or off."""
         _seqabi.check(self._lib.dn_seq_profile(self._h, int(bool(on))))
+
+    def set_graphs(self, on: bool) -> None:
+        """Decode steps replay a captured CUDA graph (default) or launch their kernels one by one."""
+        _seqabi.check(self._lib.dn_seq_set_graphs(self._h, int(bool(on))))
 
     def profile_read(self, reset: bool = True) -> Dict[str, float]:
         """Milliseconds per phase over the steps run since the last read (synchronises)."""

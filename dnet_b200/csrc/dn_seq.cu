@@ -11,6 +11,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <new>
 #include <type_traits>
 #include <vector>
@@ -84,6 +85,11 @@ struct dn_seq_model {
   CUtensorMap tm_head;
   bool tm_head_ok = false;
   unsigned int* tc_err = nullptr;   // set by a bounded in-kernel wait of the tcgen05 GEMM that ran out
+  // decode steps (every entry brings one token) replay a captured graph per (entries, wanted rows): all kernel
+  // arguments of such a step are fixed buffers, the batch description is read from the staging area
+  bool graphs_on = true;
+  std::map<std::pair<int, int>, std::pair<cudaGraphExec_t, long long>> graphs;   // -> (exec, kernels per replay)
+  float* lg_buf = nullptr;          // [8][vocab] logits of a replayed step, copied to the caller's buffer
   // phase profiler (off by default): one event at every phase boundary of a step, read back by dn_seq_profile_read
   bool prof_on = false;
   std::vector<cudaEvent_t> prof_pool;
@@ -163,6 +169,8 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
                   m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err};
   for (void* p : ptrs) if (p) cudaFree(p);
+  for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
+  if (m->lg_buf) cudaFree(m->lg_buf);
   for (auto& pm : m->prof_marks) cudaEventDestroy(pm.second);
   for (cudaEvent_t ev : m->prof_pool) cudaEventDestroy(ev);
   for (void* p : m->kpool) if (p) cudaFree(p);
@@ -262,6 +270,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   DA(m->conv_state, (size_t)cfg->max_seqs * coff * e); DA(m->delta_state, (size_t)cfg->max_seqs * doff * 4);
   m->stage_ints = 4 * MB + 3 * (size_t)(cfg->max_seqs + 1) + MB;
   DA(m->stage_d, m->stage_ints * 4); DA(m->bt_d, (size_t)cfg->max_seqs * m->max_pages * 4); DA(m->tc_err, 16);
+  DA(m->lg_buf, (size_t)8 * cfg->vocab * 4);
 #undef DA
   if (rc == DN_OK && cudaMemset(m->tc_err, 0, 16) != cudaSuccess) rc = fail(DN_ECUDA, "memset failed");
   if (rc == DN_OK && cfg->dtype == DN_SEQ_BF16) {
@@ -286,6 +295,8 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
 extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p) {
   if (!m) return fail(DN_EINVAL, "null model");
   const bool b16 = m->cfg.dtype == DN_SEQ_BF16;
+  for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);     // captured steps hold the old pointers
+  m->graphs.clear();
   if (layer < 0) {
     if (which == DN_SQ_EMBED) m->embed = p;
     else if (which == DN_SQ_FINAL_NORM) m->final_norm = p;
@@ -537,8 +548,8 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       if (P > 32) { R = 32; P = 32; }
       dim3 grid(b.E * lc.heads, (lc.vdim + 31) / 32);
       float* st = m->delta_state + l.delta_off;
-      // tokens per staged tile: two tiles of (2 dk + 34) floats each within ~36 KB of shared memory
-      const int per = 2 * lc.dim + 34, TB = std::max(1, std::min(16, 4500 / per));
+      // tokens per staged tile: two tiles of `per` floats a token within ~36 KB of shared memory
+      const int per = 2 * P * (R + 4) + 36, TB = std::max(1, std::min(16, 4500 / per));
       const size_t dsm = (size_t)2 * TB * per * 4;
 #define DR(Rv) CK(launch(k_delta_rule<Rv>, grid, dim3(32 * P), dsm, s, b, lc.heads, lc.kv_heads, lc.dim, lc.vdim, P, TB, (const float*)m->qn, \
                          (const float*)m->kn, (const float*)m->vv, (const float*)m->beta, (const float*)m->decay, st, m->delta_stride, m->od))
@@ -650,6 +661,40 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
   for (int e = 0; e < E; e++) { max_len = counts[e] > max_len ? counts[e] : max_len; row_tiles += (counts[e] + AT_ROWS - 1) / AT_ROWS; }
   Batch b{d, d + N, d + 2 * N, d + 3 * N, d + 4 * N, d + 4 * N + E + 1, d + 4 * N + 2 * E + 1, m->bt_d, N, E, m->max_pages, max_len, row_tiles};
   const int32_t* want_dev = d + 4 * N + 3 * E + 1;
-  if (m->cfg.dtype == DN_SEQ_F32) return step_T<float>(m, b, n_want, want_dev, logits, trace, s);
-  return step_T<bf16>(m, b, n_want, want_dev, logits, trace, s);
+  auto run = [&](float* lg) {
+    if (m->cfg.dtype == DN_SEQ_F32) return step_T<float>(m, b, n_want, want_dev, lg, trace, s);
+    return step_T<bf16>(m, b, n_want, want_dev, lg, trace, s);
+  };
+  // (the legacy default stream cannot be captured: steps queued on it are launched one by one)
+  const bool capturable = s != nullptr && s != cudaStreamLegacy && s != cudaStreamPerThread;
+  if (!(m->graphs_on && capturable && N == E && N <= 8 && !trace && !m->prof_on)) return run(logits);
+  // a decode step: replay (capturing at first use) the step's kernels as one graph
+  const auto key = std::make_pair(E, n_want);
+  auto it = m->graphs.find(key);
+  if (it == m->graphs.end()) {
+    const long long l0 = g_launches.load();
+    CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    const int rc = run(m->lg_buf);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ec = cudaStreamEndCapture(s, &graph);
+    if (rc != DN_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (ec != cudaSuccess) return fail(DN_ECUDA, "graph capture of a decode step failed: %s", cudaGetErrorString(ec));
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t ei = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ei != cudaSuccess) return fail(DN_ECUDA, "graph instantiation failed: %s", cudaGetErrorString(ei));
+    const long long per = g_launches.load() - l0;
+    g_launches -= per;          // captured, not run: replays are what is counted
+    it = m->graphs.emplace(key, std::make_pair(exec, per)).first;
+  }
+  CK(cudaGraphLaunch(it->second.first, s));
+  g_launches += it->second.second;
+  if (n_want > 0) CK(cudaMemcpyAsync(logits, m->lg_buf, (size_t)n_want * m->cfg.vocab * 4, cudaMemcpyDeviceToDevice, s));
+  return DN_OK;
+}
+
+extern "C" int dn_seq_set_graphs(dn_seq_model* m, int on) {
+  if (!m) return fail(DN_EINVAL, "null model");
+  m->graphs_on = on != 0;
+  return DN_OK;
 }

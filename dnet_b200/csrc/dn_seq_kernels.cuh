@@ -780,10 +780,12 @@ __global__ void k_delta_prep(DeltaPrep a, Batch b, const T* __restrict__ Uq, con
 
 // The recurrence, token by token:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
 // Columns of S are independent: a block owns 32 columns of one (entry, head); P adjacent lanes share a column,
-// each holding R = ceil(dk / P) of its rows (rows part, part + P, ...) in registers.  State [slot][head][dk][dv] fp32.
+// each holding R consecutive rows (P R >= dk) in registers.  State [slot][head][dk][dv] fp32.
 // The tokens' inputs (k, q, the block's 32 values, decay, beta) come through shared memory in tiles of TB tokens,
 // copied asynchronously one tile ahead, so that the serial chain of a token is registers, shared memory and the
-// lane shuffles only.  Sums run in an order fixed by (dk, P): four interleaved partial sums over a thread's rows,
+// lane shuffles only.  k and q lie there as P runs of R values, each run padded by 4 floats: the 16-byte reads of
+// the P lanes of a column then fall into different banks; rows from dk up are zero, so the token loop has no
+// bounds checks.  Sums run in an order fixed by (dk, P): four interleaved partial sums over a thread's rows,
 // then the lanes of a column pairwise -- nothing depends on the tile size or on where a portion was cut.
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -797,15 +799,17 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
                              const float* __restrict__ vv, const float* __restrict__ beta, const float* __restrict__ decay,
                              float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
   extern __shared__ __align__(16) float dsm[];      // 2 x TB x per
-  const int per = 2 * dk + 34;                      // k[dk] q[dk] v[32] decay beta
+  const int KP = P * (R + 4);                       // padded extent of k (and of q)
+  const int per = 2 * KP + 36;                      // k q v[32] decay beta, rounded to 16 bytes
   const int e = blockIdx.x / H, h = blockIdx.x % H, g = h / (H / G);
   const int part = threadIdx.x % P, colb = threadIdx.x / P, col = blockIdx.y * 32 + colb;
   const int s0 = b.ent_start[e], s1 = b.ent_start[e + 1];
   const bool live = col < dv;
   float* Sg = state + (size_t)b.ent_slot[e] * slot_stride + (size_t)h * dk * dv;
+  const int r0 = part * R;
   float S[R];
 #pragma unroll
-  for (int r = 0; r < R; r++) S[r] = (live && r * P + part < dk) ? Sg[(size_t)(r * P + part) * dv + col] : 0.f;
+  for (int r = 0; r < R; r++) S[r] = (live && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col] : 0.f;
   const int Cq = G * dk, Cv = H * dv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   auto stage = [&](int buf, int n0) {
@@ -815,12 +819,16 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
       float* dst = dsm + ((size_t)buf * TB + t) * per;
       const float* kr = kn + (size_t)n * Cq + g * dk;
       const float* qr = qn + (size_t)n * Cq + g * dk;
-      for (int c = lane; c < dk; c += 32) { cp_async4(dst + c, kr + c); cp_async4(dst + dk + c, qr + c); }
+      for (int c = lane; c < P * R; c += 32) {
+        const int idx = (c / R) * (R + 4) + (c % R);
+        if (c < dk) { cp_async4(dst + idx, kr + c); cp_async4(dst + KP + idx, qr + c); }
+        else dst[idx] = dst[KP + idx] = 0.f;
+      }
       const int vc = blockIdx.y * 32 + lane;
-      if (vc < dv) cp_async4(dst + 2 * dk + lane, vv + (size_t)n * Cv + h * dv + vc);
-      else dst[2 * dk + lane] = 0.f;
-      if (lane == 0) cp_async4(dst + 2 * dk + 32, decay + (size_t)n * H + h);
-      if (lane == 1) cp_async4(dst + 2 * dk + 33, beta + (size_t)n * H + h);
+      if (vc < dv) cp_async4(dst + 2 * KP + lane, vv + (size_t)n * Cv + h * dv + vc);
+      else dst[2 * KP + lane] = 0.f;
+      if (lane == 0) cp_async4(dst + 2 * KP + 32, decay + (size_t)n * H + h);
+      if (lane == 1) cp_async4(dst + 2 * KP + 33, beta + (size_t)n * H + h);
     }
     cp_async_commit();
   };
@@ -833,22 +841,33 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
     const int cnt = min(TB, s1 - n0);
     for (int t = 0; t < cnt; t++) {
       const float* in = dsm + ((size_t)buf * TB + t) * per;
-      const float gd = in[2 * dk + 32], bt = in[2 * dk + 33], v = in[2 * dk + colb];
+      const float4* k4 = reinterpret_cast<const float4*>(in + part * (R + 4));
+      const float4* q4 = reinterpret_cast<const float4*>(in + KP + part * (R + 4));
+      const float gd = in[2 * KP + 32], bt = in[2 * KP + 33], v = in[2 * KP + colb];
       float kk[R], d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < R; r++) {
-        kk[r] = r * P + part < dk ? in[r * P + part] : 0.f;
-        S[r] *= gd;
-        d4[r & 3] = fmaf(S[r], kk[r], d4[r & 3]);
+      for (int j = 0; j < R / 4; j++) {
+        const float4 kv = k4[j];
+        kk[4 * j] = kv.x; kk[4 * j + 1] = kv.y; kk[4 * j + 2] = kv.z; kk[4 * j + 3] = kv.w;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          S[4 * j + i] *= gd;
+          d4[i] = fmaf(S[4 * j + i], kk[4 * j + i], d4[i]);
+        }
       }
       float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
       for (int x = 1; x < P; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
       const float u = bt * (v - dot);
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < R; r++) {
-        S[r] = fmaf(kk[r], u, S[r]);
-        o4[r & 3] = fmaf(S[r], r * P + part < dk ? in[dk + r * P + part] : 0.f, o4[r & 3]);
+      for (int j = 0; j < R / 4; j++) {
+        const float4 qv = q4[j];
+        const float qq[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          S[4 * j + i] = fmaf(kk[4 * j + i], u, S[4 * j + i]);
+          o4[i] = fmaf(S[4 * j + i], qq[i], o4[i]);
+        }
       }
       float od = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       for (int x = 1; x < P; x <<= 1) od += __shfl_xor_sync(0xffffffffu, od, x);
@@ -858,7 +877,7 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
   }
 #pragma unroll
   for (int r = 0; r < R; r++)
-    if (live && r * P + part < dk) Sg[(size_t)(r * P + part) * dv + col] = S[r];
+    if (live && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col] = S[r];
 }
 
 // read-out of the recurrence: per head o / rms(o) * w * silu(gate) -> T.  One warp per (token, head).

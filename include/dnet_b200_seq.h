@@ -102,6 +102,11 @@ enum {
 int dn_seq_profile(dn_seq_model* m, int on);
 int dn_seq_profile_read(dn_seq_model* m, double* ms_out, int reset);
 
+/* Decode steps (every entry brings one token, at most 8 entries) replay a CUDA graph captured at the first step of
+ * each (entries, wanted rows) shape; on by default.  Off: every kernel is launched one by one (same kernels, same
+ * results).  The profiler and the layer trace always take the one-by-one path. */
+int dn_seq_set_graphs(dn_seq_model* m, int on);
+
 #ifdef __cplusplus
 }
 #endif

@@ -471,3 +471,32 @@ def test_command_lines_on_a_checkpoint_folder(tmp_path):
             if float(top[0] - top[1]) > 1e-3 * float(lg.std()):
                 assert tok == int(lg.argmax())
             seq.append(tok)
+
+
+def test_decode_graphs_replay_the_same_kernels():
+    """decode steps replay a captured graph; the launch-by-launch path gives the same bits, also after a slot and its
+    pages went to another request and with a different number of live requests"""
+    a, b = toks(90, seed=140), toks(50, seed=141)
+    outs = []
+    for graphs in (True, False):
+        with Rig(FULL, "bfloat16") as rig:
+            rig.model.set_graphs(graphs)
+            got = []
+            rig.eng.step([("a", a[:60], []), ("b", b[:30], [])])
+            for i in range(20):                                           # two live requests, one token each
+                got.append(rig.eng.step([("a", [a[60 + i]], [0]), ("b", [b[30 + i]], [0])]))
+            rig.eng.finish("b")
+            for i in range(10):                                           # one live request
+                got.append(rig.eng.step([("a", [a[80 + i]], [0])]))
+            rig.eng.finish("a")
+            rig.eng.step([("c", b[:7], [])])                             # the freed slots and pages, another request
+            for i in range(12):
+                got.append(rig.eng.step([("c", [b[7 + i]], [0])]))
+            rig.model.check()
+            outs.append(torch.cat(got).cpu())
+            if graphs:
+                ref_a, ref_b = rig.oracle(a), rig.oracle(b[:19])
+                assert err(outs[0][0:40:2], ref_a[60:80]) < TOL["bfloat16"]
+                assert err(outs[0][40:50], ref_a[80:90]) < TOL["bfloat16"]
+                assert err(outs[0][50:], ref_b[7:19]) < TOL["bfloat16"]
+    assert torch.equal(outs[0], outs[1])
