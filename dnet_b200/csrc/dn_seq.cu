@@ -543,18 +543,20 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       CK(launch(k_delta_prep<T>, dim3(N), dim3(256), (size_t)2 * l.Cq * 4, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
                 w(DN_SQ_Q_CONV), w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), (const float*)m->pa, (const float*)m->pb, w(DN_SQ_A_LOG),
                 w(DN_SQ_DT_BIAS), (const T*)cst, m->conv_stride, m->qn, m->kn, m->vv, m->beta, m->decay));
-      int R = lc.dim >= 32 ? 16 : 8, P = 1;
-      while (P * R < lc.dim) P <<= 1;
-      if (P > 32) { R = 32; P = 32; }
+      // rows a lane (R) and lanes a column (P): the smallest P R >= dk of this table
+      static const int RP[8][3] = {{8, 8, 1}, {16, 8, 2}, {32, 8, 4}, {64, 8, 8}, {128, 16, 8}, {256, 16, 16}, {512, 16, 32}, {1024, 32, 32}};
+      int R = 32, P = 32;
+      for (int i = 7; i >= 0; i--) if (lc.dim <= RP[i][0]) { R = RP[i][1]; P = RP[i][2]; }
       dim3 grid(b.E * lc.heads, (lc.vdim + 31) / 32);
       float* st = m->delta_state + l.delta_off;
       // tokens per staged tile: two tiles of `per` floats a token within ~36 KB of shared memory
       const int per = 2 * P * (R + 4) + 36, TB = std::max(1, std::min(16, 4500 / per));
       const size_t dsm = (size_t)2 * TB * per * 4;
-#define DR(Rv) CK(launch(k_delta_rule<Rv>, grid, dim3(32 * P), dsm, s, b, lc.heads, lc.kv_heads, lc.dim, lc.vdim, P, TB, (const float*)m->qn, \
-                         (const float*)m->kn, (const float*)m->vv, (const float*)m->beta, (const float*)m->decay, st, m->delta_stride, m->od))
+#define DR(Rv, Pv) if (R == Rv && P == Pv) CK(launch(k_delta_rule<Rv, Pv>, grid, dim3(32 * Pv), dsm, s, b, lc.heads, lc.kv_heads, lc.dim, lc.vdim, TB, \
+                         (const float*)m->qn, (const float*)m->kn, (const float*)m->vv, (const float*)m->beta, (const float*)m->decay, st,      \
+                         m->delta_stride, m->od))
       PH(DN_SEQ_PH_DELTA_RULE);
-      if (R == 8) DR(8); else if (R == 16) DR(16); else DR(32);
+      DR(8, 1); DR(8, 2); DR(8, 4); DR(8, 8); DR(16, 8); DR(16, 16); DR(16, 32); DR(32, 32);
 #undef DR
       PH(DN_SEQ_PH_DELTA_OUT);
       CK(launch(k_delta_out<T>, dim3(N, lc.heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_OUT_NORM), lc.heads, lc.vdim,

@@ -794,13 +794,13 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
-template <int R>
-__global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int TB, const float* __restrict__ qn, const float* __restrict__ kn,
+template <int R, int P>
+__global__ void __launch_bounds__(32 * P) k_delta_rule(Batch b, int H, int G, int dk, int dv, int TB, const float* __restrict__ qn, const float* __restrict__ kn,
                              const float* __restrict__ vv, const float* __restrict__ beta, const float* __restrict__ decay,
                              float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
   extern __shared__ __align__(16) float dsm[];      // 2 x TB x per
-  const int KP = P * (R + 4);                       // padded extent of k (and of q)
-  const int per = 2 * KP + 36;                      // k q v[32] decay beta, rounded to 16 bytes
+  constexpr int KP = P * (R + 4);                   // padded extent of k (and of q)
+  constexpr int per = 2 * KP + 36;                      // k q v[32] decay beta, rounded to 16 bytes
   const int e = blockIdx.x / H, h = blockIdx.x % H, g = h / (H / G);
   const int part = threadIdx.x % P, colb = threadIdx.x / P, col = blockIdx.y * 32 + colb;
   const int s0 = b.ent_start[e], s1 = b.ent_start[e + 1];
@@ -811,7 +811,8 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
 #pragma unroll
   for (int r = 0; r < R; r++) S[r] = (live && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col] : 0.f;
   const int Cq = G * dk, Cv = H * dv;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int nwarp = P;
   auto stage = [&](int buf, int n0) {
     const int cnt = min(TB, s1 - n0);
     for (int t = warp; t < cnt; t += nwarp) {
@@ -834,6 +835,9 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
   };
   stage(0, s0);
   int buf = 0;
+  // the read-out of token t is summed over the lanes of its column together with the dot product of token t + 1:
+  // two independent shuffle chains in flight instead of one after the other
+  float odp = 0.f;
   for (int n0 = s0; n0 < s1; n0 += TB, buf ^= 1) {
     if (n0 + TB < s1) { stage(buf ^ 1, n0 + TB); cp_async_wait<1>(); }
     else cp_async_wait<0>();
@@ -844,11 +848,12 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
       const float4* k4 = reinterpret_cast<const float4*>(in + part * (R + 4));
       const float4* q4 = reinterpret_cast<const float4*>(in + KP + part * (R + 4));
       const float gd = in[2 * KP + 32], bt = in[2 * KP + 33], v = in[2 * KP + colb];
-      float kk[R], d4[4] = {0.f, 0.f, 0.f, 0.f};
+      float kk[R], qq[R], d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < R / 4; j++) {
-        const float4 kv = k4[j];
+        const float4 kv = k4[j], qv = q4[j];
         kk[4 * j] = kv.x; kk[4 * j + 1] = kv.y; kk[4 * j + 2] = kv.z; kk[4 * j + 3] = kv.w;
+        qq[4 * j] = qv.x; qq[4 * j + 1] = qv.y; qq[4 * j + 2] = qv.z; qq[4 * j + 3] = qv.w;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
           S[4 * j + i] *= gd;
@@ -856,25 +861,27 @@ __global__ void k_delta_rule(Batch b, int H, int G, int dk, int dv, int P, int T
         }
       }
       float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-      for (int x = 1; x < P; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+#pragma unroll
+      for (int x = 1; x < P; x <<= 1) {
+        const float a = __shfl_xor_sync(0xffffffffu, dot, x), c = __shfl_xor_sync(0xffffffffu, odp, x);
+        dot += a;
+        odp += c;
+      }
+      if (live && part == 0 && n0 + t > s0) o[(size_t)(n0 + t - 1) * Cv + h * dv + col] = odp;
       const float u = bt * (v - dot);
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < R / 4; j++) {
-        const float4 qv = q4[j];
-        const float qq[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          S[4 * j + i] = fmaf(kk[4 * j + i], u, S[4 * j + i]);
-          o4[i] = fmaf(S[4 * j + i], qq[i], o4[i]);
-        }
+      for (int r = 0; r < R; r++) {
+        S[r] = fmaf(kk[r], u, S[r]);
+        o4[r & 3] = fmaf(S[r], qq[r], o4[r & 3]);
       }
-      float od = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-      for (int x = 1; x < P; x <<= 1) od += __shfl_xor_sync(0xffffffffu, od, x);
-      if (live && part == 0) o[(size_t)(n0 + t) * Cv + h * dv + col] = od;
+      odp = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     }
     __syncthreads();      // the tile is read out before the copy after next lands in it
   }
+#pragma unroll
+  for (int x = 1; x < P; x <<= 1) odp += __shfl_xor_sync(0xffffffffu, odp, x);
+  if (live && part == 0 && s1 > s0) o[(size_t)(s1 - 1) * Cv + h * dv + col] = odp;
 #pragma unroll
   for (int r = 0; r < R; r++)
     if (live && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col] = S[r];
