@@ -116,6 +116,12 @@ MECHANISMS = {
     "delta": config([delta()]),
     "delta_no_conv_one_group": config([delta(mixer={"heads": 3, "kv_heads": 3, "dim": 8, "vdim": 8, "conv": 0})]),
     "delta_wide": config([delta(mixer={"heads": 2, "kv_heads": 1, "dim": 40, "vdim": 72, "conv": 3})]),
+    "delta_dim_128": config([delta(mixer={"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 40, "conv": 2})]),
+    "delta_dim_192": config([delta(mixer={"heads": 2, "kv_heads": 2, "dim": 192, "vdim": 8, "conv": 2})]),
+    "delta_dim_320": config([delta(mixer={"heads": 1, "kv_heads": 1, "dim": 320, "vdim": 33, "conv": 0})]),
+    "delta_dim_600": config([delta(mixer={"heads": 1, "kv_heads": 1, "dim": 600, "vdim": 8, "conv": 2})]),
+    "attention_odd_sizes": config([attn(mixer={"heads": 3, "kv_heads": 1, "dim": 10, "vdim": 7, "rot": {"base": 20.0, "dims": 4}})]),
+    "attention_wide_values": config([attn(mixer={"heads": 2, "kv_heads": 1, "dim": 12, "vdim": 256})]),
     "feed_forward": config([attn(mlp=FF)]),
     "streams_1": config([attn(mlp=FF), delta()], streams=1),
     "streams_4": config([attn(mlp=FF), delta(mlp=FF)], streams=4),
@@ -500,3 +506,20 @@ def test_decode_graphs_replay_the_same_kernels():
                 assert err(outs[0][40:50], ref_a[80:90]) < TOL["bfloat16"]
                 assert err(outs[0][50:], ref_b[7:19]) < TOL["bfloat16"]
     assert torch.equal(outs[0], outs[1])
+
+
+# -- head sizes of real models: 16-byte key and value loads in decoding, MMA tiles and the wider delta-rule layouts --------
+BIG = config([
+    attn(mixer={"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 128, "conv": 2, "rot": {"base": 1000.0, "dims": 32}, "mask": {"size": 50}}),
+    attn(mixer={"heads": 2, "kv_heads": 2, "dim": 64, "vdim": 256}),
+    delta(mixer={"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 64, "conv": 3}),
+], streams=2, width=64, vocab=96)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_large_head_sizes_prompt_portions_and_decoding(dtype):
+    t = toks(330, seed=150)
+    with Rig(BIG, dtype) as rig:
+        ref = rig.oracle(t)
+        assert err(run_schedule(rig, t, [290, 17]), ref) < TOL[dtype]        # the last 23 decoded, each warp with tiles of its own
+        assert err(run_schedule(rig, t, [3, 100, 2, 200]), ref) < TOL[dtype]
