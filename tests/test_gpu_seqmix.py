@@ -523,3 +523,16 @@ def test_large_head_sizes_prompt_portions_and_decoding(dtype):
         ref = rig.oracle(t)
         assert err(run_schedule(rig, t, [290, 17]), ref) < TOL[dtype]        # the last 23 decoded, each warp with tiles of its own
         assert err(run_schedule(rig, t, [3, 100, 2, 200]), ref) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_allow_no_wide_loads(dtype):
+    """width, feed-forward and vocabulary that are multiples of neither 4 nor 8: the scalar forms of every kernel"""
+    cfg = config([attn(mixer={"conv": 3, "rot": {"base": 40.0, "dims": 6}, "mask": {"size": 33}}, mlp={"kind": "dense", "ff": 90}),
+                  delta(mlp={"kind": "dense", "ff": 45}),
+                  attn(mixer={"kv_from": 0, "mask": {"size": 20}})], streams=3, width=50, vocab=77)
+    t = toks(120, vocab=77, seed=160)
+    with Rig(cfg, dtype) as rig:
+        ref = rig.oracle(t)
+        assert err(run_schedule(rig, t, [120]), ref) < TOL[dtype]
+        assert err(run_schedule(rig, t, [70, 2, 20]), ref) < TOL[dtype]
