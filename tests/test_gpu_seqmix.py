@@ -536,3 +536,26 @@ def test_sizes_that_allow_no_wide_loads(dtype):
         ref = rig.oracle(t)
         assert err(run_schedule(rig, t, [120]), ref) < TOL[dtype]
         assert err(run_schedule(rig, t, [70, 2, 20]), ref) < TOL[dtype]
+
+
+# -- a wider model: products with many k-blocks and several tiles each way on the tcgen05 GEMM ---------------------------
+WIDER = config([
+    attn(mixer={"heads": 6, "kv_heads": 3, "dim": 64, "vdim": 32, "conv": 4, "rot": {"base": 10000.0, "dims": 32}, "mask": {"size": 128}},
+         mlp={"kind": "dense", "ff": 640}),
+    delta(mixer={"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 96, "conv": 4}, mlp={"kind": "dense", "ff": 1100}),
+    attn(mixer={"heads": 6, "kv_heads": 3, "dim": 64, "vdim": 32, "conv": 2, "rot": {"base": 10000.0, "dims": 32}, "kv_from": 0}),
+], streams=4, width=512, vocab=600, scale=1.0)
+
+
+def test_wider_model_on_the_tensor_core_products():
+    t = toks(420, vocab=600, seed=170)
+    with Rig(WIDER, "bfloat16", max_tokens=1024, max_batch_tokens=512) as rig:
+        ref = rig.oracle(t)
+        assert err(run_schedule(rig, t, [400, 3]), ref) < TOL["bfloat16"]            # 400 rows: four token tiles, a ragged last one
+        assert err(run_schedule(rig, t, [130, 33, 16, 200, 24]), ref) < TOL["bfloat16"]
+        b = toks(90, vocab=600, seed=171)
+        rig.eng.step([("b", b[:50], [])])
+        lg = rig.eng.step([("a", t[:300], [299]), ("b", b[50:], list(range(40)))])   # a mixed step of 340 rows
+        assert err(lg[:1], ref[[299]]) < TOL["bfloat16"]
+        assert err(lg[1:], rig.oracle(b)[50:]) < TOL["bfloat16"]
+        assert rig.model.check() is None
