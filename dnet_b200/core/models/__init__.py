@@ -12,6 +12,14 @@ def _subclasses(cls):
         yield from _subclasses(s)
 
 
+def ring_model_class(model_type: str):
+    """The registered class of a model type (None if there is none)."""
+    for c in _subclasses(BaseRingModel):
+        if getattr(c, "model_type", None) == model_type:
+            return c
+    return None
+
+
 def get_ring_model(model_type: str, model_config: Any, assigned_layers: Optional[List[int]] = None,
                    is_api_layer: bool = False, **kw) -> BaseRingModel:
     """subclass_where(BaseRingModel, model_type=...) of the reference (utils/loader.py:7-20)."""
@@ -22,4 +30,4 @@ def get_ring_model(model_type: str, model_config: Any, assigned_layers: Optional
 
 
 __all__ = ["BaseRingModel", "KVHandle", "LlamaRingModel", "MixtralRingModel", "MoputarRingModel", "Qwen2RingModel", "SeqHandle",
-           "SeqMixRingModel", "get_ring_model"]
+           "SeqMixRingModel", "get_ring_model", "ring_model_class"]

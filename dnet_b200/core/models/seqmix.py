@@ -90,7 +90,7 @@ class SeqMixRingModel(BaseRingModel):
 
     model_type: Optional[str] = None
     step_kernel_ok = False
-    batched_step = True        # served by shard.batching.SequenceBatcher (step function + token loop), not by the ring policies
+    batched_step = True        # ShardRuntime loads it whole and serves it with the `batched` policy over shard.batching.SequenceBatcher
 
     def __init__(self, model_config: Any, assigned_layers: Optional[List[int]] = None, is_api_layer: bool = False, *,
                  dtype: str = "bfloat16", kv_pool_pages: int = 0, max_seqs: int = 4, max_batch_tokens: int = 2048, **_ignored):

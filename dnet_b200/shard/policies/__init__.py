@@ -4,7 +4,7 @@ from typing import Type
 
 from .base import ComputePolicy, POLICY_REGISTRY, make_policy, register_policy
 from .noop import NoopPolicy
-from . import fit_in_memory, offload  # noqa: F401  (registration side effects)
+from . import batched, fit_in_memory, offload  # noqa: F401  (registration side effects)
 from .fit_in_memory import FitInMemoryPolicy
 from .offload import OffloadPolicy
 

@@ -21,7 +21,7 @@ import torch
 from dnet_b200 import _cabi
 from dnet_b200.config import get_settings
 from dnet_b200.core.memory.memory_pool import LayerAwareMemoryPool
-from dnet_b200.core.models import BaseRingModel, KVHandle, get_ring_model
+from dnet_b200.core.models import BaseRingModel, KVHandle, get_ring_model, ring_model_class
 from dnet_b200.core.types.messages import ActivationMessage
 from dnet_b200.utils.logger import logger
 from dnet_b200.utils.model import ModelMetadata, SyntheticSource, get_model_metadata, load_weight
@@ -138,6 +138,7 @@ class ShardRuntime:
         self._kv_last_seen: Dict[str, float] = {}
         self._kv_ttl_s: float = self.kv_cache_config.kv_ttl_s
         # CUDA plumbing
+        self.batcher = None                 # SequenceBatcher of a resident layer-list model (batched policy)
         self.compute_stream: Optional[torch.cuda.Stream] = None
         self.compute_stream_ptr: int = 0
         self.use_cuda_graphs: bool = bool(self._compute_settings.cuda_graphs)
@@ -249,12 +250,15 @@ class ShardRuntime:
             raise RuntimeError("dnet_b200 needs a CUDA device: the shard forward has no CPU fallback")
         self._bind_thread_device()           # load may run on an executor thread (Shard.load_model)
         self._device_index = int(torch.cuda.current_device())
+        md = get_model_metadata(req.model_path)
+        if getattr(ring_model_class(md.model_type), "batched_step", False):
+            return self._load_batched_model(req, md)      # a layer-list family: its own library, step function and policy
         _cabi.init(self._device_index)
         if self._wire_dtype_str != "bfloat16":
             raise ValueError("set DNET_TRANSPORT_WIRE_DTYPE=bf16: the wire dtype must equal the bf16 model dtype")
         lib = _cabi.load()
         lib.dn_set_option(b"pdl", 1 if self._compute_settings.pdl else 0)
-        self.model_metadata = get_model_metadata(req.model_path)
+        self.model_metadata = md
         self.assigned_layers = list(req.layers)
         self._assigned_sorted = sorted(self.assigned_layers)
         self._assigned_set = set(self._assigned_sorted)
@@ -312,6 +316,38 @@ class ShardRuntime:
         if api:
             self.model.load_weights(list(api.items()), strict=False)
         torch.cuda.synchronize()   # loads ran on torch's current stream; compute runs on compute_stream
+
+    def _load_batched_model(self, req: ShardLoadModelRequest, md) -> None:
+        """A model that runs ragged-batch steps (core/models/seqmix.py): resident whole on this shard, stepped by a
+        ``SequenceBatcher`` on the compute stream, driven frame by frame by the ``batched`` policy."""
+        from .batching import SequenceBatcher, load_model
+
+        n = int(md.num_layers)
+        if sorted(req.layers) != list(range(n)):
+            raise ValueError(f"a layer-list model is served whole by one shard: assign all {n} layers")
+        self.model_metadata = md
+        self.assigned_layers = list(req.layers)
+        self._assigned_sorted = sorted(self.assigned_layers)
+        self._assigned_set = set(self._assigned_sorted)
+        self.model_path = req.model_path
+        if self.compute_stream is None:
+            self.compute_stream = torch.cuda.Stream()
+            self.compute_stream_ptr = int(self.compute_stream.cuda_stream)
+            self.comm_stream = torch.cuda.Stream()
+        settings = get_settings()
+        per_request = int(self.kv_cache_config.max_tokens)
+        pages = int(settings.kv_cache.pool_pages) or max(1, (per_request + 63) // 64) * 8
+        self.model = load_model(req.model_path, "bfloat16", max_tokens=pages * 64, max_seqs=8,
+                                max_batch_tokens=max(64, min(per_request, 2048)))
+        self.batcher = SequenceBatcher(self.model, stream=self.compute_stream)
+        self.use_megakernel = False
+        self.use_cuda_graphs = False
+        self.policy = make_policy("batched", self, 1)
+        self.policy.configure_policy_for_model(req)
+        self.input_pool = LayerAwareMemoryPool(total_memory_mb=int(self._compute_settings.input_pool_mb), placement="pinned")
+        self.output_pool = LayerAwareMemoryPool(total_memory_mb=int(self._compute_settings.output_pool_mb), placement="pinned")
+        self._api_tensors = {}
+        torch.cuda.synchronize()
 
     def _api_tensor_to_device(self, info) -> torch.Tensor:
         src = self.model_metadata.source
@@ -375,6 +411,7 @@ class ShardRuntime:
                 self.policy = NoopPolicy(runtime=self, resident_windows=1)
                 self.model.destroy()
                 self.model = None
+                self.batcher = None
                 self.cache = None
                 self.model_metadata = None
                 self.assigned_layers = []
@@ -461,6 +498,8 @@ class ShardRuntime:
 
     def release_nonce(self, nonce: str) -> None:
         """Explicit end-of-request (the reference only has the TTL sweep)."""
+        if hasattr(self.policy, "release"):
+            self.policy.release(nonce)          # batched policy: the request's state slot and pages
         ns = self._kv_by_nonce.pop(nonce, None)
         self._kv_last_seen.pop(nonce, None)
         if ns is not None:
@@ -470,6 +509,9 @@ class ShardRuntime:
         """End of request from the transport: kernels of the nonce may still be queued on the compute
         stream, so its KV only goes back to the pool through the TTL sweep (a recycled NonceState is
         reset on the same stream, i.e. behind those kernels)."""
+        if hasattr(self.policy, "release"):
+            self.policy.release(nonce)          # stream-ordered: safe while the nonce's kernels are still queued
+            return
         self._kv_last_seen[nonce] = time.perf_counter() - float(self._kv_ttl_s) - 1.0
 
     def start(self):

@@ -559,3 +559,54 @@ def test_wider_model_on_the_tensor_core_products():
         assert err(lg[:1], ref[[299]]) < TOL["bfloat16"]
         assert err(lg[1:], rig.oracle(b)[50:]) < TOL["bfloat16"]
         assert rig.model.check() is None
+
+
+# -- through the shard runtime: load_model_core picks the batched policy, frames of tokens come back as final tokens ----
+def test_served_by_the_shard_runtime():
+    import queue
+
+    from dnet_b200.shard.models import ShardLoadModelRequest
+    from dnet_b200.shard.policies.batched import BatchedStepPolicy
+    from dnet_b200.shard.runtime import ShardRuntime
+    from dnet_b200.utils.model import HostDictSource
+    from tests.helpers import ring_generate, token_message
+
+    w = so.random_weights(FULL, 21)
+    n = len(FULL["layers"])
+    rt = ShardRuntime(shard_id="s0", queue_size=64)
+    rt.kv_cache_config.max_tokens = 256
+    rt.load_model_core(ShardLoadModelRequest(model_path=HostDictSource(w, FULL), total_layers=n, layers=list(range(n)), window_size=n,
+                                             residency_size=n, kv_bits="fp16"))
+    try:
+        assert isinstance(rt.policy, BatchedStepPolicy)
+
+        def oracle_greedy(prompt, got):
+            seq = list(prompt)
+            for tok in got:
+                lg = so.forward(FULL, w, seq)[-1]
+                top = torch.topk(lg, 2).values
+                if float(top[0] - top[1]) > 2e-2 * float(lg.std()):        # bf16 serving: only clear winners are compared
+                    assert tok == int(lg.argmax())
+                seq.append(tok)
+
+        a, b = toks(45, seed=180), toks(70, seed=181)
+        out_a = [t for t, _, _ in ring_generate([rt], "na", a, 5)]
+        oracle_greedy(a, out_a)
+        # a second request, its prompt in three chunks (the first two emit nothing), while "na" is still live
+        for part in (b[:30], b[30:64]):
+            rt.policy.process(token_message(rt, "nb", part, more=True))
+            with pytest.raises(queue.Empty):
+                rt.activation_send_queue.get_nowait()
+        out_b = [t for t, _, _ in ring_generate([rt], "nb", b[64:], 4)]
+        oracle_greedy(b, out_b)
+        assert rt.model.free_slots == 6
+        rt.release_nonce("na")
+        rt.release_nonce_deferred("nb")
+        assert rt.model.free_slots == 8 and rt.model.free_pages == rt.model.pool_pages
+        # a partial assignment is refused
+        rt2 = ShardRuntime(shard_id="s1", queue_size=8)
+        with pytest.raises(ValueError):
+            rt2.load_model_core(ShardLoadModelRequest(model_path=HostDictSource(w, FULL), total_layers=n, layers=[0, 1], window_size=2,
+                                                      residency_size=2, kv_bits="fp16"))
+    finally:
+        assert rt.unload_model_core().success
