@@ -675,7 +675,10 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
   auto it = m->graphs.find(key);
   if (it == m->graphs.end()) {
     const long long l0 = g_launches.load();
-    CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      cudaGetLastError();          // this stream cannot be captured now (e.g. it is part of the caller's own capture): launch one by one
+      return run(logits);
+    }
     const int rc = run(m->lg_buf);
     cudaGraph_t graph = nullptr;
     const cudaError_t ec = cudaStreamEndCapture(s, &graph);
