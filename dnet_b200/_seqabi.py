@@ -14,28 +14,46 @@ _ROOT = Path(__file__).resolve().parent
 HEADER_PATH = _ROOT.parent / "include" / "dnet_b200_seq.h"
 
 DN_SEQ_BF16, DN_SEQ_F32 = 0, 1
-DN_MIX_ATTENTION, DN_MIX_DELTA = 0, 1
+DN_MIX_ATTENTION, DN_MIX_DELTA, DN_MIX_PARALLEL, DN_MIX_WKV = 0, 1, 2, 3
+DN_NORM_RMS, DN_NORM_DYT = 0, 1
+DN_MLP_DENSE, DN_MLP_MOE = 0, 1
 # dn_seq_bind slots, in the header's order
 _LAYER_SLOTS = ["norm1", "norm2", "mix.q", "mix.k", "mix.v", "mix.o", "mix.q.conv", "mix.k.conv", "mix.v.conv", "mix.q.norm",
                 "mix.k.norm", "mix.a", "mix.b", "mix.g", "mix.A_log", "mix.dt_bias", "mix.norm", "mlp.gate", "mlp.up", "mlp.down",
-                "hc1.in", "hc1.out", "hc1.mix", "hc2.in", "hc2.out", "hc2.mix"]
+                "hc1.in", "hc1.out", "hc1.mix", "hc2.in", "hc2.out", "hc2.mix",
+                "norm1.b", "norm1.alpha", "norm2.b", "norm2.alpha",
+                "post1", "post1.b", "post1.alpha", "post2", "post2.b", "post2.alpha",
+                "sink", "head_gate",
+                "r.q", "r.k", "r.v", "r.g", "r.o", "r.norm",
+                "decay1", "decay2", "decay.b",
+                "mu.r", "mu.k", "mu.v", "mu.g", "mu.w", "bonus",
+                "router", "router.b", "shared.gate", "shared.up", "shared.down"]
 LAYER_SLOT = {n: i for i, n in enumerate(_LAYER_SLOTS)}
-MODEL_SLOT = {"embed": 100, "final.norm": 101, "head": 102}
+MODEL_SLOT = {"embed": 100, "final.norm": 101, "head": 102, "final.norm.b": 103, "final.norm.alpha": 104,
+              "embed.norm": 105, "embed.norm.b": 106, "embed.norm.alpha": 107, "loop.in": 108}
+EXPERT_SLOT = {"gate": 0, "up": 1, "down": 2}
 # phases of a step, in the header's order (dn_seq_profile_read)
 PHASES = ["embed", "norm", "proj", "attn_prep", "attn", "delta_prep", "delta_rule", "delta_out", "conv_carry", "out_proj",
-          "write_back", "ff_up", "ff_down", "head", "other"]
+          "write_back", "ff_up", "ff_down", "head", "other", "recur_prep", "recur", "recur_out", "router", "moe_up", "moe_down"]
 
 
 class LayerCfg(C.Structure):
     _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
                 ("conv", C.c_int32), ("chunk", C.c_int32), ("rot_dims", C.c_int32), ("rot_base", C.c_float), ("scale", C.c_float),
-                ("kv_from", C.c_int32), ("ff", C.c_int32)]
+                ("kv_from", C.c_int32), ("ff", C.c_int32),
+                ("qk_norm", C.c_int32), ("softcap", C.c_float), ("sink", C.c_int32), ("out_gate", C.c_int32),
+                ("r_heads", C.c_int32), ("r_dim", C.c_int32), ("r_vdim", C.c_int32), ("rank", C.c_int32), ("tau", C.c_float),
+                ("left_scale", C.c_float), ("right_scale", C.c_float),
+                ("mlp_kind", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32), ("limit", C.c_float),
+                ("shared_ff", C.c_int32), ("shared_limit", C.c_float)]
 
 
 class SeqCfg(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("streams", C.c_int32), ("dtype", C.c_int32),
                 ("eps", C.c_float), ("embed_scale", C.c_float), ("pool_pages", C.c_int32), ("max_seqs", C.c_int32),
-                ("max_batch_tokens", C.c_int32)]
+                ("max_batch_tokens", C.c_int32),
+                ("norm_kind", C.c_int32), ("post_norm", C.c_int32), ("embed_norm", C.c_int32), ("logit_softcap", C.c_float),
+                ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32)]
 
 
 def declared_symbols() -> List[str]:
@@ -52,6 +70,8 @@ _PROTOS = {
     "dn_seq_model_create": (_i, [C.POINTER(SeqCfg), C.POINTER(LayerCfg), C.POINTER(_vp)]),
     "dn_seq_model_destroy": (_i, [_vp]),
     "dn_seq_bind": (_i, [_vp, _i, _i, _vp]),
+    "dn_seq_bind_expert": (_i, [_vp, _i, _i, _i, _vp]),
+    "dn_seq_layer_runs": (_i, [_vp]),
     "dn_seq_open": (_i, [_vp, _vp, C.POINTER(_i)]),
     "dn_seq_close": (_i, [_vp, _i]),
     "dn_seq_length": (_i, [_vp, _i]),

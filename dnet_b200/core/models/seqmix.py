@@ -19,16 +19,35 @@ the counterpart of ``KVHandle``.
 
 Absent keys switch a mechanism off (no ``streams``: plain residual; no ``mask``: plain causal; no ``rot``: no
 rotation; no ``conv``: no convolution; no ``kv_from``: own keys and values).
+
+``FilinexRingModel`` reads the same kind of list with other mixers and a routed feed-forward:
+
+    {"architecture": "Filinex", "vocab": V, "width": W, "norm": {"eps": e}, "logit_softcap": c,
+     "loop": {"start": a, "stop": b, "times": n},                                  # optional
+     "layers": [{"type": "parallel",
+                 "mixer": {"left": {"heads", "kv_heads", "dim", "vdim", "scale", "softcap"},
+                           "right": {"heads", "dim", "vdim", "tau"}, "left_scale", "right_scale"},
+                 "mlp": {"kind": "moe", "router": {"experts", "top"}, "expert": {"ff", "limit"},
+                         "shared": {"ff", "limit"} | null} | null},
+                {"type": "wkv", "mixer": {"heads", "dim"}, "mlp": ...}, ...]}
+
+Sizes the config does not give (the inner size of the two-step decay projections, a wkv layer's value size) are
+read from the checkpoint's tensor shapes (``tensor_shapes``), or from the optional keys ``rank`` / ``vdim``.
 """
 from __future__ import annotations
 
 import ctypes as C
+import re
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from dnet_b200 import _seqabi
 from .base import BaseRingModel, _stream_ptr
+
+
+_LAYER_KEY = re.compile(r"^l\d+\.")
+_EXPERT_KEY = re.compile(r"^mlp\.e(\d+)\.(gate|up|down)$")
 
 
 class SeqHandle:
@@ -50,38 +69,99 @@ class SeqHandle:
         self.slot = -1
 
 
-def parse_layer_list(cfg: dict) -> Tuple[_seqabi.SeqCfg, List[_seqabi.LayerCfg]]:
-    """config.json of a layer-list family -> the C structs (every size and constant comes from the config)."""
+def _attention_cfg(lc: _seqabi.LayerCfg, mx: dict, qk_norm: bool) -> None:
+    lc.scale = float(mx.get("scale", float(mx["dim"]) ** -0.5))
+    lc.chunk = int((mx.get("mask") or {}).get("size", 0))
+    rot = mx.get("rot") or {}
+    lc.rot_dims = int(rot.get("dims", 0))
+    lc.rot_base = float(rot.get("base", 10000.0))
+    lc.kv_from = int(mx["kv_from"]) if mx.get("kv_from") is not None else -1
+    lc.qk_norm = int(qk_norm)
+    lc.softcap = float(mx.get("softcap", 0.0) or 0.0)
+    lc.heads, lc.kv_heads = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"]))
+    lc.dim, lc.vdim = int(mx["dim"]), int(mx.get("vdim", mx["dim"]))
+    lc.conv = int(mx.get("conv", 0) or 0)
+
+
+def parse_layer_list(cfg: dict, family: Optional[dict] = None,
+                     shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> Tuple[_seqabi.SeqCfg, List[_seqabi.LayerCfg]]:
+    """config.json of a layer-list family -> the C structs.  Every size and constant comes from the config, or (what
+    the config does not give) from a tensor's shape; ``family`` holds what a design fixes (kind of norm, norms after a
+    sublayer and on the embedding, whether attention norms q and k, has a sink, gates its heads)."""
+    fam = {"norm": "rms", "post_norm": False, "embed_norm": False, "qk_norm": True, "sink": False, "head_gate": False}
+    fam.update(family or {})
+    shapes = shapes or {}
+
+    def from_shape(name: str, axis: int, mx: dict, key: str, what: str) -> int:
+        if mx.get(key) is not None:
+            return int(mx[key])
+        if name in shapes:
+            return int(shapes[name][axis])
+        raise ValueError(f"{what}: the config has no {key!r} and the checkpoint's shape of {name} is not known")
+
     layers = []
     for i, L in enumerate(cfg["layers"]):
         mx = L["mixer"]
         kind = L["type"]
         lc = _seqabi.LayerCfg()
+        lc.kv_from = -1
         if kind == "attention":
             lc.mixer = _seqabi.DN_MIX_ATTENTION
-            lc.scale = float(mx.get("scale", float(mx["dim"]) ** -0.5))
-            lc.chunk = int((mx.get("mask") or {}).get("size", 0))
-            rot = mx.get("rot") or {}
-            lc.rot_dims = int(rot.get("dims", 0))
-            lc.rot_base = float(rot.get("base", 10000.0))
-            lc.kv_from = int(mx["kv_from"]) if mx.get("kv_from") is not None else -1
+            _attention_cfg(lc, mx, fam["qk_norm"])
+            lc.sink, lc.out_gate = int(fam["sink"]), int(fam["head_gate"])
         elif kind == "delta":
             lc.mixer = _seqabi.DN_MIX_DELTA
-            lc.kv_from = -1
+            lc.heads, lc.kv_heads = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"]))
+            lc.dim, lc.vdim = int(mx["dim"]), int(mx.get("vdim", mx["dim"]))
+            lc.conv = int(mx.get("conv", 0) or 0)
+        elif kind == "parallel":
+            lc.mixer = _seqabi.DN_MIX_PARALLEL
+            _attention_cfg(lc, mx["left"], fam["qk_norm"])
+            lc.sink, lc.out_gate = int(fam["sink"]), int(fam["head_gate"])
+            r = mx["right"]
+            lc.r_heads, lc.r_dim, lc.r_vdim = int(r["heads"]), int(r["dim"]), int(r.get("vdim", r["dim"]))
+            lc.tau = float(r["tau"])
+            lc.rank = from_shape(f"l{i}.mix.right.a1", 0, r, "rank", f"layer {i}")
+            lc.left_scale, lc.right_scale = float(mx.get("left_scale", 1.0)), float(mx.get("right_scale", 1.0))
+        elif kind == "wkv":
+            lc.mixer = _seqabi.DN_MIX_WKV
+            lc.heads = lc.kv_heads = int(mx["heads"])
+            lc.dim = int(mx["dim"])
+            if mx.get("vdim") is not None:
+                lc.vdim = int(mx["vdim"])
+            elif f"l{i}.mix.v" in shapes:
+                lc.vdim = int(shapes[f"l{i}.mix.v"][0]) // lc.heads
+            else:
+                lc.vdim = lc.dim
+            lc.rank = from_shape(f"l{i}.mix.w1", 0, mx, "rank", f"layer {i}")
         else:
             raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
-        lc.heads, lc.kv_heads = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"]))
-        lc.dim, lc.vdim = int(mx["dim"]), int(mx.get("vdim", mx["dim"]))
-        lc.conv = int(mx.get("conv", 0) or 0)
         mlp = L.get("mlp")
         if mlp:
-            if mlp.get("kind", "dense") != "dense":
-                raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} unsupported")
-            lc.ff = int(mlp["ff"])
+            mk = mlp.get("kind", "dense")
+            if mk == "dense":
+                lc.mlp_kind, lc.ff = _seqabi.DN_MLP_DENSE, int(mlp["ff"])
+            elif mk == "moe":
+                lc.mlp_kind = _seqabi.DN_MLP_MOE
+                lc.ff, lc.limit = int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
+                lc.experts, lc.top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
+                sh = mlp.get("shared")
+                if sh:
+                    lc.shared_ff, lc.shared_limit = int(sh["ff"]), float(sh["limit"])
+            else:
+                raise ValueError(f"layer {i}: feed-forward kind {mk!r} unsupported")
         layers.append(lc)
     sc = _seqabi.SeqCfg(width=int(cfg["width"]), vocab=int(cfg["vocab"]), n_layers=len(layers), streams=int(cfg.get("streams", 0) or 0),
                         eps=float((cfg.get("norm") or {}).get("eps", 1e-6)),
                         embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)))
+    sc.norm_kind = _seqabi.DN_NORM_DYT if fam["norm"] == "dyt" else _seqabi.DN_NORM_RMS
+    sc.post_norm, sc.embed_norm = int(fam["post_norm"]), int(fam["embed_norm"])
+    sc.logit_softcap = float(cfg.get("logit_softcap", 0.0) or 0.0)
+    lp = cfg.get("loop")
+    if lp:
+        sc.loop_start, sc.loop_stop, sc.loop_times = int(lp["start"]), int(lp["stop"]), int(lp["times"])
+        if sc.loop_times < 1:
+            raise ValueError("loop.times must be at least 1")
     return sc, layers
 
 
@@ -89,16 +169,20 @@ class SeqMixRingModel(BaseRingModel):
     """A whole layer-list model on one GPU: owns cache pool + state slots, runs ragged-batch steps."""
 
     model_type: Optional[str] = None
+    family: Dict[str, Any] = {}            # what the design fixes (parse_layer_list)
+    # checkpoint name of a layer's tensor -> the library's name, per mixer type ("*" for every layer)
+    tensor_alias: Dict[str, Dict[str, str]] = {}
     step_kernel_ok = False
     batched_step = True        # ShardRuntime loads it whole and serves it with the `batched` policy over shard.batching.SequenceBatcher
 
     def __init__(self, model_config: Any, assigned_layers: Optional[List[int]] = None, is_api_layer: bool = False, *,
-                 dtype: str = "bfloat16", kv_pool_pages: int = 0, max_seqs: int = 4, max_batch_tokens: int = 2048, **_ignored):
+                 dtype: str = "bfloat16", kv_pool_pages: int = 0, max_seqs: int = 4, max_batch_tokens: int = 2048,
+                 tensor_shapes: Optional[Dict[str, Tuple[int, ...]]] = None, **_ignored):
         if is_api_layer and assigned_layers:
             raise RuntimeError("API layer doesn't handle layers")
         self.config = dict(model_config)
         self.model_config = model_config
-        sc, layers = parse_layer_list(self.config)
+        sc, layers = parse_layer_list(self.config, self.family, tensor_shapes)
         n = len(layers)
         if assigned_layers is not None and sorted(assigned_layers) != list(range(n)):
             raise ValueError("a layer-list model is served whole by one shard: its layers share pages (kv_from) and fp32 "
@@ -120,6 +204,7 @@ class SeqMixRingModel(BaseRingModel):
         self._h = h.value
         self._cfg_struct, self._layer_structs = sc, layers
         self.layers = list(range(n))
+        self.layer_runs = int(self._lib.dn_seq_layer_runs(self._h))
         self.abs_to_local = {i: i for i in self.layers}
         self.hidden_size, self.vocab_size = int(sc.width), int(sc.vocab)
         self.max_seqs, self.max_batch_tokens, self.pool_pages = int(sc.max_seqs), int(sc.max_batch_tokens), int(sc.pool_pages)
@@ -129,15 +214,30 @@ class SeqMixRingModel(BaseRingModel):
     def expected_tensors(self) -> Dict[str, Tuple[int, ...]]:
         """Checkpoint name -> shape, from the config alone."""
         W, V, S = self.hidden_size, self.vocab_size, int(self._cfg_struct.streams)
+        sc = self._cfg_struct
+        dyt = sc.norm_kind == _seqabi.DN_NORM_DYT
         out: Dict[str, Tuple[int, ...]] = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+
+        def norm(name: str) -> None:
+            out[name] = (W,)
+            if dyt:
+                out[name + ".b"], out[name + ".alpha"] = (W,), ()
+
+        norm("final.norm")
+        if sc.embed_norm:
+            norm("embed.norm")
+        if sc.loop_times > 0:
+            out["loop.in"] = (W, 2 * W)
         for i, lc in enumerate(self._layer_structs):
             p = f"l{i}."
-            att = lc.mixer == _seqabi.DN_MIX_ATTENTION
-            cq = (lc.heads if att else lc.kv_heads) * lc.dim
+            att = lc.mixer in (_seqabi.DN_MIX_ATTENTION, _seqabi.DN_MIX_PARALLEL)
+            cq = (lc.heads if lc.mixer != _seqabi.DN_MIX_DELTA else lc.kv_heads) * lc.dim
             ck, cv = lc.kv_heads * lc.dim, (lc.kv_heads if att else lc.heads) * lc.vdim
             co = lc.heads * lc.vdim
             own = not (att and lc.kv_from >= 0)
-            out[p + "norm1"] = (W,)
+            norm(p + "norm1")
+            if sc.post_norm:
+                norm(p + "post1")
             out[p + "mix.q"] = (cq, W)
             out[p + "mix.o"] = (W, co)
             if own:
@@ -147,18 +247,46 @@ class SeqMixRingModel(BaseRingModel):
                 if own:
                     out[p + "mix.k.conv"], out[p + "mix.v.conv"] = (ck, lc.conv), (cv, lc.conv)
             if att:
-                out[p + "mix.q.norm"] = (cq,)
-                if own:
-                    out[p + "mix.k.norm"] = (ck,)
-            else:
+                if lc.qk_norm:
+                    out[p + "mix.q.norm"] = (cq,)
+                    if own:
+                        out[p + "mix.k.norm"] = (ck,)
+                if lc.sink:
+                    out[p + "sink"] = (lc.heads,)
+                if lc.out_gate:
+                    out[p + "head_gate"] = (lc.heads, W)
+            if lc.mixer == _seqabi.DN_MIX_PARALLEL:
+                rc, rv = lc.r_heads * lc.r_dim, lc.r_heads * lc.r_vdim
+                out[p + "r.q"] = out[p + "r.k"] = (rc, W)
+                out[p + "r.v"] = out[p + "r.g"] = (rv, W)
+                out[p + "r.o"], out[p + "r.norm"] = (W, rv), (lc.r_vdim,)
+                out[p + "decay1"], out[p + "decay2"], out[p + "decay.b"] = (lc.rank, W), (rc, lc.rank), (rc,)
+            elif lc.mixer == _seqabi.DN_MIX_WKV:
+                for q in "rkvgw":
+                    out[p + "mu." + q] = (W,)
+                out[p + "mix.g"], out[p + "mix.norm"] = (co, W), (co,)
+                out[p + "decay1"], out[p + "decay2"], out[p + "decay.b"] = (lc.rank, W), (cq, lc.rank), (cq,)
+                out[p + "bonus"] = (lc.heads, lc.dim)
+            elif lc.mixer == _seqabi.DN_MIX_DELTA:
                 out[p + "mix.a"] = out[p + "mix.b"] = (lc.heads, W)
                 out[p + "mix.g"] = (co, W)
                 out[p + "mix.A_log"] = out[p + "mix.dt_bias"] = (lc.heads,)
                 out[p + "mix.norm"] = (lc.vdim,)
             if lc.ff > 0:
-                out[p + "norm2"] = (W,)
-                out[p + "mlp.gate"] = out[p + "mlp.up"] = (lc.ff, W)
-                out[p + "mlp.down"] = (W, lc.ff)
+                norm(p + "norm2")
+                if sc.post_norm:
+                    norm(p + "post2")
+                if lc.mlp_kind == _seqabi.DN_MLP_MOE:
+                    out[p + "router"], out[p + "router.b"] = (lc.experts, W), (lc.experts,)
+                    for e in range(lc.experts):
+                        out[f"{p}mlp.e{e}.gate"] = out[f"{p}mlp.e{e}.up"] = (lc.ff, W)
+                        out[f"{p}mlp.e{e}.down"] = (W, lc.ff)
+                    if lc.shared_ff > 0:
+                        out[p + "shared.gate"] = out[p + "shared.up"] = (lc.shared_ff, W)
+                        out[p + "shared.down"] = (W, lc.shared_ff)
+                else:
+                    out[p + "mlp.gate"] = out[p + "mlp.up"] = (lc.ff, W)
+                    out[p + "mlp.down"] = (W, lc.ff)
             if S > 0:
                 for q in ("hc1", "hc2") if lc.ff > 0 else ("hc1",):
                     out[p + q + ".in"] = out[p + q + ".out"] = (S,)
@@ -178,6 +306,11 @@ class SeqMixRingModel(BaseRingModel):
             if key.startswith("layers."):
                 _, idx, rest = key.split(".", 2)
                 key = f"l{idx}.{rest}"
+            if self.tensor_alias and _LAYER_KEY.match(key):
+                lname, suffix = key.split(".", 1)
+                kind = self.config["layers"][int(lname[1:])]["type"]
+                suffix = self.tensor_alias.get(kind, {}).get(suffix, self.tensor_alias.get("*", {}).get(suffix, suffix))
+                key = f"{lname}.{suffix}"
             shape = want.get(key)
             if shape is None:
                 if strict:
@@ -191,7 +324,12 @@ class SeqMixRingModel(BaseRingModel):
                 _seqabi.check(self._lib.dn_seq_bind(self._h, -1, _seqabi.MODEL_SLOT[key], t.data_ptr()))
             else:
                 lname, suffix = key.split(".", 1)
-                _seqabi.check(self._lib.dn_seq_bind(self._h, int(lname[1:]), _seqabi.LAYER_SLOT[suffix], t.data_ptr()))
+                ex = _EXPERT_KEY.match(suffix)
+                if ex:
+                    _seqabi.check(self._lib.dn_seq_bind_expert(self._h, int(lname[1:]), int(ex.group(1)), _seqabi.EXPERT_SLOT[ex.group(2)],
+                                                               t.data_ptr()))
+                else:
+                    _seqabi.check(self._lib.dn_seq_bind(self._h, int(lname[1:]), _seqabi.LAYER_SLOT[suffix], t.data_ptr()))
             self._bound[key] = t     # keep the borrowed memory alive
         return self
 
@@ -214,7 +352,7 @@ class SeqMixRingModel(BaseRingModel):
              layer_trace: bool = False):
         """One batched step.  entries: (sequence, its next tokens); want: rows of the concatenated tokens whose
         logits are returned as fp32 [len(want), vocab] (None if empty).  With layer_trace also the residual after
-        every layer, fp32 [layers, N, width]."""
+        every layer run (a layer inside a loop counts each time), fp32 [layer runs, N, width]."""
         E = len(entries)
         slots = (C.c_int32 * E)(*[h.slot for h, _ in entries])
         counts = (C.c_int32 * E)(*[len(t) for _, t in entries])
@@ -225,7 +363,7 @@ class SeqMixRingModel(BaseRingModel):
         wr = (C.c_int32 * max(1, nw))(*[int(x) for x in want])
         dev = torch.device("cuda", self.device)
         logits = torch.empty(nw, self.vocab_size, dtype=torch.float32, device=dev) if nw else None
-        trace = torch.empty(len(self.layers), N, self.hidden_size, dtype=torch.float32, device=dev) if layer_trace else None
+        trace = torch.empty(self.layer_runs, N, self.hidden_size, dtype=torch.float32, device=dev) if layer_trace else None
         _seqabi.check(self._lib.dn_seq_step(self._h, E, slots, counts, toks, nw, wr, logits.data_ptr() if nw else None,
                                             trace.data_ptr() if layer_trace else None, _stream_ptr(stream)))
         return (logits, trace) if layer_trace else logits
@@ -293,3 +431,28 @@ class MoputarRingModel(SeqMixRingModel):
     gated delta-rule layers, short convolutions on q / k / v, hyper-connected residual streams."""
 
     model_type = "moputar"
+
+
+_NORM_ALIAS = {f"{a}{x}": f"{b}{x}" for a, b in (("norm1b", "post1"), ("norm2b", "post2")) for x in ("", ".b", ".alpha")}
+_MOE_ALIAS = {"mlp.router": "router", "mlp.router.b": "router.b", "mlp.shared.gate": "shared.gate", "mlp.shared.up": "shared.up",
+              "mlp.shared.down": "shared.down"}
+
+
+class FilinexRingModel(SeqMixRingModel):
+    """Filinex: every norm a dynamic tanh, before and after each sublayer and on the embedding; layers are either a
+    parallel mixer (softmax attention with capped scores, a sink and gated heads beside a gated linear attention with
+    a decay per key channel) or a wkv mixer (token-shift mixing, decayed state read with a bonus for the current
+    token); routed clamped-GLU experts with a shared one; a span of layers that runs several times with the
+    embedding fed back in before each pass; capped logits."""
+
+    model_type = "filinex"
+    family = {"norm": "dyt", "post_norm": True, "embed_norm": True, "qk_norm": False, "sink": True, "head_gate": True}
+    tensor_alias = {
+        "*": {**_NORM_ALIAS, **_MOE_ALIAS},
+        "parallel": {"mix.left.q": "mix.q", "mix.left.k": "mix.k", "mix.left.v": "mix.v", "mix.left.o": "mix.o", "mix.left.sink": "sink",
+                     "mix.left.g": "head_gate", "mix.right.q": "r.q", "mix.right.k": "r.k", "mix.right.v": "r.v", "mix.right.g": "r.g",
+                     "mix.right.o": "r.o", "mix.right.norm": "r.norm", "mix.right.a1": "decay1", "mix.right.a2": "decay2",
+                     "mix.right.a2.b": "decay.b"},
+        "wkv": {"mix.r": "mix.q", "mix.mu.r": "mu.r", "mix.mu.k": "mu.k", "mix.mu.v": "mu.v", "mix.mu.g": "mu.g", "mix.mu.w": "mu.w",
+                "mix.w1": "decay1", "mix.w2": "decay2", "mix.w0": "decay.b", "mix.u": "bonus"},
+    }

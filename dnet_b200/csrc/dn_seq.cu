@@ -2,6 +2,8 @@
 // bound weight pointers, the page pool and the state slots, the staging of a step's batch description, and the
 // launch sequence of a layer.  All arithmetic is in dn_seq_kernels.cuh.
 #include "dn_seq_kernels.cuh"
+#include "dn_seq_recur.cuh"
+#include "dn_seq_moe.cuh"
 #include "dn_gemm_tc.cuh"      // the tcgen05 / TMA GEMM the llama-family prefill runs on (namespace dn)
 #include "../../include/dnet_b200_seq.h"
 
@@ -56,22 +58,40 @@ struct SeqLayer {
   CUtensorMap tm[DN_SQ_COUNT];
   bool tm_ok[DN_SQ_COUNT];
   XMaps x_mo, x_act;            // the mixer's output buffer [MB, Co] and the feed-forward's [MB, ff]
+  XMaps x_mo_r, x_lr;           // the linear-attention half's [MB, Rv]; the decay projection's inner [MB, rank]
   int Cq, Ck, Cv, Co;           // projection widths: q, k, v and the mixer's output before W_o
-  int kv_index;                 // attention: which page pool (own or the one it borrows); -1 for delta
-  size_t conv_off, delta_off;   // element offsets into a slot's carried conv inputs / fp32 delta state
+  int Rc, Rv;                   // linear-attention half of a parallel mixer: q / k width, v / output width
   float* inv_freq;              // [rot/2] device
+  std::vector<const void*> etab_h;   // routed experts: [3][E] gate, up, down
+  const void** etab_d;
+};
+// One run of a layer.  A layer inside the loop runs loop_times times on the same weights; every run has its own
+// pages, carried inputs and recurrent state.
+struct Run {
+  int layer;
+  bool inject;                  // a pass of the loop starts here: x <- W_in [x; x0] first
+  int kv_index;                 // attention: which page pool (own or the one it borrows); -1 without attention
+  size_t conv_off, state_off;   // element offsets into a slot's carried inputs (conv taps, shifted row) / fp32 state
 };
 
 struct dn_seq_model {
   dn_seq_cfg cfg;
   std::vector<SeqLayer> L;
+  std::vector<Run> runs;
   const void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
+  const void* mw[16] = {nullptr};     // the other model tensors, by (which - DN_SQ_EMBED)
+  CUtensorMap tm_loop_in;
+  bool tm_loop_ok = false;
+  XMaps x_cat, x_xm[SHIFT_MAX];
   size_t esz = 2;
   int S1 = 1, MB = 0, max_pages = 0;
   // scratch
   float *xs = nullptr, *y = nullptr, *pa = nullptr, *pb = nullptr, *qn = nullptr, *kn = nullptr, *vv = nullptr, *od = nullptr,
-        *beta = nullptr, *decay = nullptr;
-  void *h = nullptr, *uq = nullptr, *uk = nullptr, *uv = nullptr, *qb = nullptr, *mo = nullptr, *gt = nullptr, *act = nullptr;
+        *beta = nullptr, *decay = nullptr, *y2 = nullptr, *x0 = nullptr, *dz = nullptr, *rwt = nullptr, *eo = nullptr;
+  void *h = nullptr, *uq = nullptr, *uk = nullptr, *uv = nullptr, *qb = nullptr, *mo = nullptr, *gt = nullptr, *act = nullptr, *cat = nullptr,
+       *xm = nullptr, *lr = nullptr, *eact = nullptr;
+  int32_t *ridx = nullptr, *rpos = nullptr, *rtok = nullptr, *tiles = nullptr;
+  int max_tiles = 0;
   // state
   std::vector<void*> kpool, vpool;
   void* conv_state = nullptr;
@@ -167,7 +187,8 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   if (!m) return DN_OK;
   cudaDeviceSynchronize();
   void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
-                  m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err};
+                  m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err, m->y2, m->x0, m->dz, m->rwt,
+                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles};
   for (void* p : ptrs) if (p) cudaFree(p);
   for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
   if (m->lg_buf) cudaFree(m->lg_buf);
@@ -175,7 +196,7 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   for (cudaEvent_t ev : m->prof_pool) cudaEventDestroy(ev);
   for (void* p : m->kpool) if (p) cudaFree(p);
   for (void* p : m->vpool) if (p) cudaFree(p);
-  for (auto& l : m->L) if (l.inv_freq) cudaFree(l.inv_freq);
+  for (auto& l : m->L) { if (l.inv_freq) cudaFree(l.inv_freq); if (l.etab_d) cudaFree((void*)l.etab_d); }
   if (m->stage_h) cudaFreeHost(m->stage_h);
   if (m->bt_h) cudaFreeHost(m->bt_h);
   if (m->staged) cudaEventDestroy(m->staged);
@@ -198,23 +219,30 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   m->MB = cfg->max_batch_tokens;
   m->max_pages = cfg->pool_pages;
   m->L.resize(cfg->n_layers);
-  int mq = 1, mk = 1, mv = 1, mo = 1, mh = 1, mff = 1, mdq = 1;
-  size_t coff = 0, doff = 0;
+  int mq = 1, mk = 1, mv = 1, mo = 1, mh = 1, mff = 1, mdq = 1, mrank = 1, mpairs = 0, meff = 1, mexp = 1;
+  bool any_wkv = false;
   int rc = DN_OK;
+  const bool looped = cfg->loop_times > 0;
+  if (looped && (cfg->loop_start < 0 || cfg->loop_stop > cfg->n_layers || cfg->loop_start >= cfg->loop_stop))
+    rc = fail(DN_EINVAL, "loop [%d, %d) x %d does not fit %d layers", cfg->loop_start, cfg->loop_stop, cfg->loop_times, cfg->n_layers);
+  if (rc == DN_OK && cfg->norm_kind != DN_NORM_RMS && cfg->norm_kind != DN_NORM_DYT) rc = fail(DN_EINVAL, "norm kind %d unknown", cfg->norm_kind);
+  if (rc == DN_OK && cfg->norm_kind == DN_NORM_RMS && (cfg->post_norm || cfg->embed_norm))
+    rc = fail(DN_EINVAL, "norms after a sublayer and on the embedding exist as dynamic tanh only");
   for (int i = 0; i < cfg->n_layers && rc == DN_OK; i++) {
     SeqLayer& l = m->L[i];
     l.c = layers[i];
     memset(l.w, 0, sizeof(l.w));
     memset(l.tm_ok, 0, sizeof(l.tm_ok));
     l.inv_freq = nullptr;
-    l.kv_index = -1;
+    l.etab_d = nullptr;
+    l.Rc = l.Rv = 0;
     const dn_seq_layer_cfg& c = l.c;
     if (c.heads <= 0 || c.kv_heads <= 0 || c.heads % c.kv_heads || c.dim <= 0 || c.vdim <= 0) {
       rc = fail(DN_EINVAL, "layer %d: heads %d / kv_heads %d / dim %d / vdim %d unsupported", i, c.heads, c.kv_heads, c.dim, c.vdim);
       break;
     }
     if (c.conv < 0 || c.conv > 9) { rc = fail(DN_EINVAL, "layer %d: conv taps %d unsupported (0..9)", i, c.conv); break; }
-    if (c.mixer == DN_MIX_ATTENTION) {
+    if (c.mixer == DN_MIX_ATTENTION || c.mixer == DN_MIX_PARALLEL) {
       if (c.vdim > 256) { rc = fail(DN_EINVAL, "layer %d: vdim %d > 256", i, c.vdim); break; }
       if (c.rot_dims < 0 || c.rot_dims > c.dim || (c.rot_dims & 1)) { rc = fail(DN_EINVAL, "layer %d: rot dims %d unsupported", i, c.rot_dims); break; }
       l.Cq = c.heads * c.dim;
@@ -225,16 +253,10 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
           rc = fail(DN_EINVAL, "layer %d: kv_from %d must name an earlier attention layer with its own keys and the same head sizes", i, c.kv_from);
           break;
         }
-        l.kv_index = m->L[c.kv_from].kv_index;
         l.Ck = l.Cv = 0;
       } else {
         l.Ck = c.kv_heads * c.dim;
         l.Cv = c.kv_heads * c.vdim;
-        l.kv_index = (int)m->kpool.size();
-        m->kpool.push_back(nullptr);
-        m->vpool.push_back(nullptr);
-        if ((rc = dalloc(&m->kpool.back(), (size_t)cfg->pool_pages * PAGE * l.Ck * m->esz)) != DN_OK) break;
-        if ((rc = dalloc(&m->vpool.back(), (size_t)cfg->pool_pages * PAGE * l.Cv * m->esz)) != DN_OK) break;
       }
       if (c.rot_dims > 0) {
         std::vector<float> f(c.rot_dims / 2);
@@ -242,21 +264,90 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
         if ((rc = dalloc(&l.inv_freq, f.size() * 4)) != DN_OK) break;
         if (cudaMemcpy(l.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) { rc = fail(DN_ECUDA, "inv_freq upload failed"); break; }
       }
+      if (c.mixer == DN_MIX_PARALLEL) {
+        if (c.r_heads <= 0 || c.r_dim <= 0 || c.r_dim > 1024 || c.r_vdim <= 0 || c.rank <= 0 || !(c.tau > 0.f)) {
+          rc = fail(DN_EINVAL, "layer %d: linear-attention half heads %d / dim %d / vdim %d / rank %d / tau %g unsupported", i, c.r_heads, c.r_dim, c.r_vdim, c.rank, c.tau);
+          break;
+        }
+        if (c.conv > 0 || c.kv_from >= 0) { rc = fail(DN_EINVAL, "layer %d: a parallel mixer has neither convolutions nor borrowed keys", i); break; }
+        l.Rc = c.r_heads * c.r_dim;
+        l.Rv = c.r_heads * c.r_vdim;
+        mdq = std::max(mdq, l.Rc);
+        mrank = std::max(mrank, c.rank);
+        mh = std::max(mh, c.r_heads);
+      }
     } else if (c.mixer == DN_MIX_DELTA) {
       if (c.dim > 1024) { rc = fail(DN_EINVAL, "layer %d: delta dim %d > 1024", i, c.dim); break; }
       l.Cq = l.Ck = c.kv_heads * c.dim;
       l.Cv = l.Co = c.heads * c.vdim;
-      l.delta_off = doff;
-      doff += (size_t)c.heads * c.dim * c.vdim;
       mdq = std::max(mdq, l.Cq);
+    } else if (c.mixer == DN_MIX_WKV) {
+      if (c.dim > 1024 || c.rank <= 0 || c.conv > 0) { rc = fail(DN_EINVAL, "layer %d: wkv dim %d / rank %d / conv %d unsupported", i, c.dim, c.rank, c.conv); break; }
+      l.Cq = l.Ck = c.heads * c.dim;
+      l.Cv = l.Co = c.heads * c.vdim;
+      mdq = std::max(mdq, l.Cq);
+      mrank = std::max(mrank, c.rank);
+      any_wkv = true;
     } else {
       rc = fail(DN_EINVAL, "layer %d: mixer %d unknown", i, c.mixer);
       break;
     }
-    l.conv_off = coff;
-    if (c.conv > 1) coff += (size_t)(c.conv - 1) * (l.Cq + l.Ck + l.Cv);
-    mq = std::max(mq, l.Cq); mk = std::max(mk, l.Ck); mv = std::max(mv, l.Cv); mo = std::max(mo, l.Co);
-    mh = std::max(mh, c.heads); mff = std::max(mff, c.ff);
+    if (c.mlp_kind == DN_MLP_MOE && c.ff > 0) {
+      if (c.experts <= 0 || c.experts > 4096 || c.top <= 0 || c.top > 16 || c.top > c.experts || c.shared_ff < 0) {
+        rc = fail(DN_EINVAL, "layer %d: %d experts / top %d unsupported (top <= 16, <= experts)", i, c.experts, c.top);
+        break;
+      }
+      l.etab_h.assign((size_t)3 * c.experts, nullptr);
+      if ((rc = dalloc(&l.etab_d, (size_t)3 * c.experts * sizeof(void*))) != DN_OK) break;
+      mpairs = std::max(mpairs, c.top);
+      meff = std::max(meff, c.ff);
+      mexp = std::max(mexp, c.experts);
+      mff = std::max(mff, c.shared_ff);
+    } else if (c.mlp_kind != DN_MLP_DENSE && c.ff > 0) {
+      rc = fail(DN_EINVAL, "layer %d: feed-forward kind %d unknown", i, c.mlp_kind);
+      break;
+    } else {
+      mff = std::max(mff, c.ff);
+    }
+    mq = std::max(mq, std::max(l.Cq, l.Rc)); mk = std::max(mk, std::max(l.Ck, l.Rc)); mv = std::max(mv, std::max(l.Cv, l.Rv));
+    mo = std::max(mo, std::max(l.Co, l.Rv));
+    mh = std::max(mh, c.heads);
+  }
+  // the order of layer runs, and every run's own pages and state
+  size_t coff = 0, doff = 0;
+  if (rc == DN_OK) {
+    std::vector<std::pair<int, bool>> order;
+    for (int i = 0; i < cfg->n_layers; i++) {
+      if (looped && i == cfg->loop_start) {
+        for (int t = 0; t < cfg->loop_times; t++)
+          for (int j = cfg->loop_start; j < cfg->loop_stop; j++) order.emplace_back(j, j == cfg->loop_start);
+        i = cfg->loop_stop - 1;
+      } else order.emplace_back(i, false);
+    }
+    std::vector<int> last_run(cfg->n_layers, -1);
+    for (auto& o : order) {
+      Run r{o.first, o.second, -1, 0, 0};
+      const SeqLayer& l = m->L[r.layer];
+      const dn_seq_layer_cfg& c = l.c;
+      if (c.mixer == DN_MIX_ATTENTION || c.mixer == DN_MIX_PARALLEL) {
+        if (c.kv_from >= 0) r.kv_index = m->runs[last_run[c.kv_from]].kv_index;
+        else {
+          r.kv_index = (int)m->kpool.size();
+          m->kpool.push_back(nullptr);
+          m->vpool.push_back(nullptr);
+          if ((rc = dalloc(&m->kpool.back(), (size_t)cfg->pool_pages * PAGE * l.Ck * m->esz)) != DN_OK) break;
+          if ((rc = dalloc(&m->vpool.back(), (size_t)cfg->pool_pages * PAGE * l.Cv * m->esz)) != DN_OK) break;
+        }
+      }
+      r.conv_off = coff;
+      if (c.conv > 1) coff += (size_t)(c.conv - 1) * (l.Cq + l.Ck + l.Cv);
+      if (c.mixer == DN_MIX_WKV) coff += (size_t)cfg->width;       // the previous token's input row
+      r.state_off = doff;
+      if (c.mixer == DN_MIX_DELTA || c.mixer == DN_MIX_WKV) doff += (size_t)c.heads * c.dim * c.vdim;
+      if (c.mixer == DN_MIX_PARALLEL) doff += (size_t)c.r_heads * c.r_dim * c.r_vdim;
+      last_run[r.layer] = (int)m->runs.size();
+      m->runs.push_back(r);
+    }
   }
   const size_t MB = m->MB, W = cfg->width, e = m->esz;
   m->conv_stride = coff;
@@ -265,6 +356,15 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   DA(m->xs, (size_t)m->S1 * MB * W * 4); DA(m->y, MB * W * 4); DA(m->pa, MB * mh * 4); DA(m->pb, MB * mh * 4);
   DA(m->qn, MB * mdq * 4); DA(m->kn, MB * mdq * 4); DA(m->vv, MB * mo * 4); DA(m->od, MB * mo * 4);
   DA(m->beta, MB * mh * 4); DA(m->decay, MB * mh * 4);
+  DA(m->y2, MB * W * 4); DA(m->dz, MB * mdq * 4); DA(m->lr, MB * mrank * e);
+  if (looped) { DA(m->x0, MB * W * 4); DA(m->cat, MB * 2 * W * e); }
+  if (any_wkv) DA(m->xm, (size_t)SHIFT_MAX * MB * W * e);
+  if (mpairs > 0) {
+    const size_t P = MB * mpairs;
+    m->max_tiles = (int)(P / MOE_ROWS) + mexp + 1;
+    DA(m->ridx, P * 4); DA(m->rpos, P * 4); DA(m->rtok, P * 4); DA(m->rwt, P * 4); DA(m->tiles, ((size_t)3 * m->max_tiles + 4) * 4);
+    DA(m->eact, P * meff * e); DA(m->eo, P * W * 4);
+  }
   DA(m->h, MB * W * e); DA(m->uq, MB * mq * e); DA(m->uk, MB * mk * e); DA(m->uv, MB * mv * e); DA(m->qb, MB * mq * e);
   DA(m->mo, MB * mo * e); DA(m->gt, MB * mo * e); DA(m->act, MB * mff * e);
   DA(m->conv_state, (size_t)cfg->max_seqs * coff * e); DA(m->delta_state, (size_t)cfg->max_seqs * doff * 4);
@@ -277,8 +377,13 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
     make_xmaps(&m->x_h, m->h, m->MB, cfg->width);
     for (auto& l : m->L) {
       make_xmaps(&l.x_mo, m->mo, m->MB, l.Co);
-      if (l.c.ff > 0) make_xmaps(&l.x_act, m->act, m->MB, l.c.ff);
+      if (l.Rv > 0) make_xmaps(&l.x_mo_r, m->mo, m->MB, l.Rv);
+      if (l.c.rank > 0) make_xmaps(&l.x_lr, m->lr, m->MB, l.c.rank);
+      const int fa = l.c.mlp_kind == DN_MLP_MOE ? l.c.shared_ff : l.c.ff;
+      if (fa > 0) make_xmaps(&l.x_act, m->act, m->MB, fa);
     }
+    if (m->cat) make_xmaps(&m->x_cat, m->cat, m->MB, 2 * cfg->width);
+    if (m->xm) for (int i = 0; i < SHIFT_MAX; i++) make_xmaps(&m->x_xm[i], (char*)m->xm + (size_t)i * MB * W * e, m->MB, cfg->width);
   }
   if (rc == DN_OK && cudaHostAlloc((void**)&m->stage_h, m->stage_ints * 4, cudaHostAllocPortable) != cudaSuccess) rc = fail(DN_ENOMEM, "pinned staging failed");
   if (rc == DN_OK && cudaHostAlloc((void**)&m->bt_h, (size_t)cfg->max_seqs * m->max_pages * 4, cudaHostAllocPortable) != cudaSuccess) rc = fail(DN_ENOMEM, "pinned block table failed");
@@ -303,6 +408,9 @@ extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p)
     else if (which == DN_SQ_HEAD) {
       m->head = p;
       m->tm_head_ok = b16 && make_tmap(&m->tm_head, p, m->cfg.vocab, m->cfg.width, dn::TC_BM);
+    } else if (which > DN_SQ_HEAD && which <= DN_SQ_LOOP_IN) {
+      m->mw[which - DN_SQ_EMBED] = p;
+      if (which == DN_SQ_LOOP_IN) m->tm_loop_ok = b16 && make_tmap(&m->tm_loop_in, p, m->cfg.width, 2 * m->cfg.width, dn::TC_BM);
     } else return fail(DN_EINVAL, "tensor %d is not a model tensor", which);
     return DN_OK;
   }
@@ -319,11 +427,36 @@ extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p)
     case DN_SQ_GATE: case DN_SQ_UP: rows = l.c.ff; break;
     case DN_SQ_O: rows = m->cfg.width; cols = l.Co; break;
     case DN_SQ_DOWN: rows = m->cfg.width; cols = l.c.ff; break;
+    case DN_SQ_HEAD_GATE: rows = l.c.heads; break;
+    case DN_SQ_R_Q: case DN_SQ_R_K: rows = l.Rc; break;
+    case DN_SQ_R_V: case DN_SQ_R_G: rows = l.Rv; break;
+    case DN_SQ_R_O: rows = m->cfg.width; cols = l.Rv; break;
+    case DN_SQ_DECAY1: rows = l.c.rank; break;
+    case DN_SQ_DECAY2: rows = l.c.mixer == DN_MIX_PARALLEL ? l.Rc : l.Cq; cols = l.c.rank; break;
+    case DN_SQ_SH_GATE: case DN_SQ_SH_UP: rows = l.c.shared_ff; break;
+    case DN_SQ_SH_DOWN: rows = m->cfg.width; cols = l.c.shared_ff; break;
     default: break;
   }
+  if (l.c.mlp_kind == DN_MLP_MOE && (which == DN_SQ_GATE || which == DN_SQ_UP || which == DN_SQ_DOWN))
+    return fail(DN_EINVAL, "layer %d: the matrices of routed experts are bound with dn_seq_bind_expert", layer);
   l.tm_ok[which] = b16 && rows > 0 && make_tmap(&l.tm[which], p, rows, cols, dn::TC_BM);
   return DN_OK;
 }
+
+extern "C" int dn_seq_bind_expert(dn_seq_model* m, int layer, int expert, int which, const void* p) {
+  if (!m) return fail(DN_EINVAL, "null model");
+  if (layer < 0 || layer >= (int)m->L.size()) return fail(DN_EINVAL, "layer %d out of range", layer);
+  SeqLayer& l = m->L[layer];
+  if (l.c.mlp_kind != DN_MLP_MOE || l.c.ff <= 0) return fail(DN_EINVAL, "layer %d has no routed experts", layer);
+  if (expert < 0 || expert >= l.c.experts || which < DN_SQ_E_GATE || which > DN_SQ_E_DOWN) return fail(DN_EINVAL, "expert %d / matrix %d out of range", expert, which);
+  for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
+  m->graphs.clear();
+  const size_t at = (size_t)which * l.c.experts + expert;
+  l.etab_h[at] = p;
+  CK(cudaMemcpy((void*)(l.etab_d + at), &p, sizeof(void*), cudaMemcpyHostToDevice));
+  return DN_OK;
+}
+extern "C" int dn_seq_layer_runs(dn_seq_model* m) { return m ? (int)m->runs.size() : DN_EINVAL; }
 
 extern "C" int dn_seq_open(dn_seq_model* m, dn_seq_stream s, int* slot_out) {
   if (!m || !slot_out) return fail(DN_EINVAL, "null argument");
@@ -412,14 +545,14 @@ static cudaError_t gemm_tc(const CUtensorMap& w, const CUtensorMap& w2, const XM
   return launch_tc<32, EPI, (two ? 5 : 8)>(w, w2, x.m[0], p, s);
 }
 
-// One product Y[N, O] = X[N, K] W[O, K]^T (act: gelu_tanh(X W^T) * (X W2^T)).  bf16 batches of 16 tokens and more run on
+// One product Y[N, O] = X[N, K] W[O, K]^T (act: an ACT_* epilogue, the two-operand ones on X W^T and X W2^T).  bf16 batches of 16 tokens and more run on
 // the tcgen05 GEMM when the operands have TMA descriptors; a few rows (decode) on the weight-streaming row kernel;
 // everything else, and all of fp32, on the CUDA-core tiles.
 struct LinMaps { const CUtensorMap* w; const CUtensorMap* w2; const XMaps* x; };
 template <class T>
 static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32,
-                          int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}) {
-  if (std::is_same<T, bf16>::value && N >= 16 && O >= 32 && tm.w && tm.x && tm.x->ok && (!act || tm.w2)) {
+                          int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}, float alim = 0.f) {
+  if (std::is_same<T, bf16>::value && N >= 16 && O >= 32 && tm.w && tm.x && tm.x->ok && (act == ACT_NONE || (act == ACT_GEGLU && tm.w2))) {
     dn::TcParams p;
     memset(&p, 0, sizeof(p));
     p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err;
@@ -429,12 +562,12 @@ static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const voi
   }
   if (N <= 8) {
     dim3 grid((O + 7) / 8);
-    if (out32) return launch(k_linear_rows<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
-    return launch(k_linear_rows<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
+    if (out32) return launch(k_linear_rows<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
+    return launch(k_linear_rows<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
   }
   dim3 grid((O + 63) / 64, (N + 63) / 64);
-  if (out32) return launch(k_linear<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
-  return launch(k_linear<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act);
+  if (out32) return launch(k_linear<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
+  return launch(k_linear<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
 }
 
 // Attention of a step: bf16 steps that bring a prompt portion (an entry of 16 tokens or more) run on the MMA tiles when
@@ -445,7 +578,7 @@ static bool attn_tiles_ok(const dn_seq_layer_cfg& lc, const Batch& b) {
 }
 template <int DKP, int DVP>
 static cudaError_t attn_tiles_launch(cudaStream_t s, const Batch& b, const bf16* q, const bf16* kp, const bf16* vp, const dn_seq_layer_cfg& lc,
-                                     bf16* out) {
+                                     const AttnExtra& ex, bf16* out) {
   constexpr size_t smem = ((size_t)2 * AT_ROWS * (DKP + 8) + (size_t)AT_ROWS * (DVP + 8)) * 2;
   static bool attr = false;
   if (!attr) {
@@ -454,12 +587,13 @@ static cudaError_t attn_tiles_launch(cudaStream_t s, const Batch& b, const bf16*
     attr = true;
   }
   g_launches++;
-  k_attn_tiles<DKP, DVP><<<dim3(b.row_tiles, lc.heads), 128, smem, s>>>(b, q, kp, vp, lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, out);
+  k_attn_tiles<DKP, DVP><<<dim3(b.row_tiles, lc.heads), 128, smem, s>>>(b, q, kp, vp, lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, ex, out);
   return cudaGetLastError();
 }
-static cudaError_t attn_tiles(cudaStream_t s, const Batch& b, const bf16* q, const bf16* kp, const bf16* vp, const dn_seq_layer_cfg& lc, bf16* out) {
+static cudaError_t attn_tiles(cudaStream_t s, const Batch& b, const bf16* q, const bf16* kp, const bf16* vp, const dn_seq_layer_cfg& lc,
+                              const AttnExtra& ex, bf16* out) {
   const int kq = lc.dim <= 32 ? 0 : lc.dim <= 64 ? 1 : 2, vq = lc.vdim <= 32 ? 0 : lc.vdim <= 64 ? 1 : 2;
-#define AT(a, c, A, Cc) if (kq == a && vq == c) return attn_tiles_launch<A, Cc>(s, b, q, kp, vp, lc, out);
+#define AT(a, c, A, Cc) if (kq == a && vq == c) return attn_tiles_launch<A, Cc>(s, b, q, kp, vp, lc, ex, out);
   AT(0, 0, 32, 32) AT(0, 1, 32, 64) AT(0, 2, 32, 128) AT(1, 0, 64, 32) AT(1, 1, 64, 64) AT(1, 2, 64, 128)
   AT(2, 0, 128, 32) AT(2, 1, 128, 64) AT(2, 2, 128, 128)
 #undef AT
@@ -476,63 +610,156 @@ static cudaError_t mark(dn_seq_model* m, int phase, cudaStream_t s) {
   return cudaEventRecord(ev, s);
 }
 
+// the expert products of a routed feed-forward: h [N, W] -> m->y [N, W] (routed sum), m->y2 (shared expert, if any)
+template <class T>
+static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
+  const dn_seq_layer_cfg& lc = l.c;
+  const int W = m->cfg.width, E = lc.experts, top = lc.top, P = N * top;
+  auto w = [&](int i) { return (const T*)l.w[i]; };
+  auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
+  CK(mark(m, DN_SEQ_PH_ROUTER, s));
+  CK(launch(k_router<T>, dim3(N), dim3(128), (size_t)E * 4, s, (const T*)m->h, w(DN_SQ_ROUTER), w(DN_SQ_ROUTER_B), W, E, top, m->ridx, m->rwt, m->rpos));
+  if (N <= 8) {
+    CK(mark(m, DN_SEQ_PH_MOE_UP, s));
+    CK(launch(k_moe_rows<T, true>, dim3((lc.ff + 7) / 8, P), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, (const int32_t*)m->ridx, top,
+              m->eact, lc.ff, W, lc.limit));
+    CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
+    CK(launch(k_moe_rows<T, false>, dim3((W + 7) / 8, P), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, (const int32_t*)m->ridx, top,
+              m->eo, W, lc.ff, 0.f));
+  } else {
+    MoePlan pl{m->rpos, m->rtok, m->tiles, m->tiles + m->max_tiles, m->tiles + 2 * m->max_tiles, m->tiles + 3 * m->max_tiles};
+    const int mt = std::min(m->max_tiles, P / MOE_ROWS + E + 1);
+    CK(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)(2 * E + 1) * 4, s, (const int32_t*)m->ridx, P, top, E, pl));
+    CK(mark(m, DN_SEQ_PH_MOE_UP, s));
+    CK(launch(k_moe_tiles<T, true>, dim3((lc.ff + 63) / 64, mt), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, pl, m->eact, lc.ff, W, lc.limit));
+    CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
+    CK(launch(k_moe_tiles<T, false>, dim3((W + 63) / 64, mt), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, pl, m->eo, W, lc.ff, 0.f));
+  }
+  CK(launch(k_moe_combine, dim3((unsigned)(((size_t)N * W + 255) / 256)), dim3(256), 0, s, (const float*)m->eo, (const float*)m->rwt, (const int32_t*)m->rpos, N, W, top, m->y));
+  if (lc.shared_ff > 0) {
+    CK(mark(m, DN_SEQ_PH_FF_UP, s));
+    CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_SH_GATE], l.w[DN_SQ_SH_UP], m->act, N, lc.shared_ff, W, false, ACT_CGLU,
+                 LinMaps{wm(DN_SQ_SH_GATE), wm(DN_SQ_SH_UP), &m->x_h}, lc.shared_limit));
+    CK(mark(m, DN_SEQ_PH_FF_DOWN, s));
+    CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_SH_DOWN], nullptr, m->y2, N, W, lc.shared_ff, true, 0, LinMaps{wm(DN_SQ_SH_DOWN), nullptr, &l.x_act}));
+  }
+  return DN_OK;
+}
+
+// rows a lane (R) and lanes a column (P) of the recurrences: the smallest P R >= dk of this table
+static void recur_shape(int dk, int* R, int* P) {
+  static const int RP[8][3] = {{8, 8, 1}, {16, 8, 2}, {32, 8, 4}, {64, 8, 8}, {128, 16, 8}, {256, 16, 16}, {512, 16, 32}, {1024, 32, 32}};
+  *R = 32; *P = 32;
+  for (int i = 7; i >= 0; i--) if (dk <= RP[i][0]) { *R = RP[i][1]; *P = RP[i][2]; }
+}
+// a decayed outer-product recurrence over the step's entries: inputs m->qn / kn / vv / dz (fp32), output m->od
+static int decay_rule(dn_seq_model* m, const Batch& b, int mode, int H, int dk, int dv, const void* bonus, float* st, cudaStream_t s) {
+  int R, P;
+  recur_shape(dk, &R, &P);
+  dim3 grid(b.E * H, (dv + 31) / 32);
+  const int per = 3 * P * (R + 4) + 32, TB = std::max(1, std::min(16, 4500 / per));
+  const size_t dsm = (size_t)2 * TB * per * 4;
+#define DR(Rv, Pv) if (R == Rv && P == Pv) CK(launch(k_decay_rule<Rv, Pv>, grid, dim3(32 * Pv), dsm, s, mode, b, H, dk, dv, TB, (const float*)m->qn, \
+                         (const float*)m->kn, (const float*)m->vv, (const float*)m->dz, bonus, m->esz == 4 ? 1 : 0, st, m->delta_stride, m->od))
+  DR(8, 1); DR(8, 2); DR(8, 4); DR(8, 8); DR(16, 8); DR(16, 16); DR(16, 32); DR(32, 32);
+#undef DR
+  return DN_OK;
+}
+
 template <class T>
 static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* want_dev, float* logits, float* trace, cudaStream_t s) {
   const dn_seq_cfg& c = m->cfg;
   const int N = b.N, W = c.width, S = c.streams, S1 = m->S1;
+  const size_t NW = (size_t)N * W;
   const size_t nsm = ((size_t)W + 40) * 4;
-  const int ew = (int)(((size_t)N * W + 255) / 256), ew4 = (int)(((size_t)N * W / 4 + 255) / 256);
+  const int ew = (int)((NW + 255) / 256), ew4 = (int)((NW / 4 + 255) / 256);
   const dim3 nthr(W >= 4096 ? 512 : W >= 2048 ? 256 : 128);     // threads of a norm block: a function of the width only
+  const bool dyt = c.norm_kind == DN_NORM_DYT;
+  auto mwp = [&](int which) { return (const T*)m->mw[which - DN_SQ_EMBED]; };
   auto write_back = [&](const T* mix, const T* out) {
     if (W % 4 == 0) return launch(k_write_back<T, 4>, dim3(ew4), dim3(256), 0, s, m->xs, N, W, S, mix, out, (const float*)m->y);
     return launch(k_write_back<T, 1>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, mix, out, (const float*)m->y);
   };
+  // a sublayer's output a y (+ b y2) joins the residual, through the norm after the sublayer where the model has one
+  auto join = [&](SeqLayer& l, int post, int hc_mix, int hc_out, float a, const float* y2, float bb) -> cudaError_t {
+    auto w = [&](int i) { return (const T*)l.w[i]; };
+    if (c.post_norm) {
+      if (S <= 0) return launch(k_dyt_add<T>, dim3(ew), dim3(256), 0, s, m->xs, NW, W, (const float*)m->y, a, y2, bb, w(post), w(post + 1), w(post + 2));
+      cudaError_t e = launch(k_dyt_inplace<T>, dim3(ew), dim3(256), 0, s, m->y, NW, W, a, y2, bb, w(post), w(post + 1), w(post + 2));
+      if (e != cudaSuccess) return e;
+    } else if (y2 || a != 1.f) {
+      cudaError_t e = launch(k_axpby, dim3(ew), dim3(256), 0, s, m->y, NW, a, y2 ? y2 : (const float*)m->y, y2 ? bb : 0.f);
+      if (e != cudaSuccess) return e;
+    }
+    return write_back(w(hc_mix), w(hc_out));
+  };
 #define PH(id) CK(mark(m, id, s))
   PH(DN_SEQ_PH_EMBED);
-  CK(launch(k_embed<T>, dim3(N), dim3(128), 0, s, (const T*)m->embed, b, c.embed_scale, W, S1, m->xs));
-  for (int li = 0; li < c.n_layers; li++) {
-    SeqLayer& l = m->L[li];
+  CK(launch(k_embed<T>, dim3(N), dim3(128), 0, s, (const T*)m->embed, b, c.embed_scale, W, S1, m->xs, mwp(DN_SQ_EMBED_NORM), mwp(DN_SQ_EMBED_NORM_B),
+            c.embed_norm ? mwp(DN_SQ_EMBED_NORM_ALPHA) : (const T*)nullptr, m->x0));
+  for (int ri = 0; ri < (int)m->runs.size(); ri++) {
+    const Run& run = m->runs[ri];
+    SeqLayer& l = m->L[run.layer];
     const dn_seq_layer_cfg& lc = l.c;
     auto w = [&](int i) { return (const T*)l.w[i]; };
+    auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
+    if (run.inject) {       // a pass of the loop starts: x <- W_in [x; x0]
+      PH(DN_SEQ_PH_OTHER);
+      CK(launch(k_loop_cat<T>, dim3((unsigned)((2 * NW + 255) / 256)), dim3(256), 0, s, (const float*)m->xs, (const float*)m->x0, N, W, (T*)m->cat));
+      CK(linear<T>(m, s, (const T*)m->cat, m->mw[DN_SQ_LOOP_IN - DN_SQ_EMBED], nullptr, m->xs, N, W, 2 * W, true, 0,
+                   LinMaps{m->tm_loop_ok ? &m->tm_loop_in : nullptr, nullptr, &m->x_cat}));
+    }
     // ---- mixer sublayer
     PH(DN_SEQ_PH_NORM);
-    CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
-    T* cst = (T*)m->conv_state + l.conv_off;
-    auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
-    PH(DN_SEQ_PH_PROJ);
+    CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
+              w(DN_SQ_NORM1_B), dyt ? w(DN_SQ_NORM1_ALPHA) : (const T*)nullptr));
+    T* cst = (T*)m->conv_state + run.conv_off;
+    float* st = m->delta_state + run.state_off;
     const bool few = N <= 8;      // a decode step: all projections of the mixer in one launch of the row kernel
-    if (few) {
-      LinSegs sg;
-      memset(&sg, 0, sizeof(sg));
-      auto add = [&](int which, void* y, int rows, int o32) {
-        if (rows <= 0) return;
-        sg.W[sg.n] = l.w[which]; sg.Y[sg.n] = y; sg.O[sg.n] = rows; sg.out32[sg.n] = o32; sg.n++;
-      };
-      add(DN_SQ_Q, m->uq, l.Cq, 0); add(DN_SQ_K, m->uk, l.Ck, 0); add(DN_SQ_V, m->uv, l.Cv, 0);
-      if (lc.mixer == DN_MIX_DELTA) { add(DN_SQ_A, m->pa, lc.heads, 1); add(DN_SQ_B, m->pb, lc.heads, 1); add(DN_SQ_G, m->gt, l.Co, 0); }
+    float ja = 1.f, jb = 0.f;
+    const float* jy2 = nullptr;
+    LinSegs sg;
+    memset(&sg, 0, sizeof(sg));
+    auto add = [&](const void* x, int which, void* y, int rows, int o32) {
+      if (rows <= 0) return;
+      sg.X[sg.n] = x; sg.W[sg.n] = l.w[which]; sg.Y[sg.n] = y; sg.O[sg.n] = rows; sg.out32[sg.n] = o32; sg.n++;
+    };
+    auto run_segs = [&]() {
       int blocks = 0;
       for (int i = 0; i < sg.n; i++) blocks += (sg.O[i] + 7) / 8;
-      CK(launch(k_linear_rows_multi<T>, dim3(blocks), dim3(256), 0, s, (const T*)m->h, sg, N, W));
-    } else {
-      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &m->x_h}));
-      if (l.Ck) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_K), nullptr, &m->x_h}));
-      if (l.Cv) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_h}));
+      return launch(k_linear_rows_multi<T>, dim3(blocks), dim3(256), 0, s, (const T*)m->h, sg, N, W);
+    };
+    if (lc.mixer == DN_MIX_ATTENTION || lc.mixer == DN_MIX_DELTA || lc.mixer == DN_MIX_PARALLEL) {
+      PH(DN_SEQ_PH_PROJ);
+      if (few) {
+        add(nullptr, DN_SQ_Q, m->uq, l.Cq, 0); add(nullptr, DN_SQ_K, m->uk, l.Ck, 0); add(nullptr, DN_SQ_V, m->uv, l.Cv, 0);
+        if (lc.mixer == DN_MIX_DELTA) { add(nullptr, DN_SQ_A, m->pa, lc.heads, 1); add(nullptr, DN_SQ_B, m->pb, lc.heads, 1); add(nullptr, DN_SQ_G, m->gt, l.Co, 0); }
+        if (lc.mixer != DN_MIX_DELTA && lc.out_gate) add(nullptr, DN_SQ_HEAD_GATE, m->pa, lc.heads, 1);
+        CK(run_segs());
+      } else {
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &m->x_h}));
+        if (l.Ck) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_K), nullptr, &m->x_h}));
+        if (l.Cv) CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_h}));
+        if (lc.mixer != DN_MIX_DELTA && lc.out_gate)
+          CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_HEAD_GATE], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_HEAD_GATE), nullptr, &m->x_h}));
+      }
     }
-    if (lc.mixer == DN_MIX_ATTENTION) {
-      AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, c.eps, l.inv_freq};
+    if (lc.mixer == DN_MIX_ATTENTION || lc.mixer == DN_MIX_PARALLEL) {
+      AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, lc.qk_norm, c.eps, l.inv_freq};
+      AttnExtra ex{lc.softcap, lc.sink ? l.w[DN_SQ_SINK] : nullptr, lc.out_gate ? (const float*)m->pa : nullptr};
       const size_t sm = ((size_t)l.Cq + l.Ck + 40) * 4;
       PH(DN_SEQ_PH_ATTN_PREP);
       CK(launch(k_attn_prep<T>, dim3(N), dim3(256), sm, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_Q_CONV),
                 w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), w(DN_SQ_Q_NORM), w(DN_SQ_K_NORM), (const T*)cst, m->conv_stride, (T*)m->qb,
-                (T*)m->kpool[l.kv_index], (T*)m->vpool[l.kv_index]));
+                (T*)m->kpool[run.kv_index], (T*)m->vpool[run.kv_index]));
       PH(DN_SEQ_PH_ATTN);
       if (attn_tiles_ok<T>(lc, b))
-        CK(attn_tiles(s, b, (const bf16*)m->qb, (const bf16*)m->kpool[l.kv_index], (const bf16*)m->vpool[l.kv_index], lc, (bf16*)m->mo));
+        CK(attn_tiles(s, b, (const bf16*)m->qb, (const bf16*)m->kpool[run.kv_index], (const bf16*)m->vpool[run.kv_index], lc, ex, (bf16*)m->mo));
       else
         CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(AT_WARPS * 32), (size_t)(((lc.dim + 3) & ~3) + AT_WARPS * (2 + (lc.vdim + 31) / 32 * 32)) * 4, s, b,
-                  (const T*)m->qb, (const T*)m->kpool[l.kv_index],
-                  (const T*)m->vpool[l.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, (T*)m->mo));
-    } else {
+                  (const T*)m->qb, (const T*)m->kpool[run.kv_index],
+                  (const T*)m->vpool[run.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, ex, (T*)m->mo));
+    } else if (lc.mixer == DN_MIX_DELTA) {
       if (!few) {
         CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));
         CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_B], nullptr, m->pb, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_B), nullptr, &m->x_h}));
@@ -543,12 +770,9 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       CK(launch(k_delta_prep<T>, dim3(N), dim3(256), (size_t)2 * l.Cq * 4, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
                 w(DN_SQ_Q_CONV), w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), (const float*)m->pa, (const float*)m->pb, w(DN_SQ_A_LOG),
                 w(DN_SQ_DT_BIAS), (const T*)cst, m->conv_stride, m->qn, m->kn, m->vv, m->beta, m->decay));
-      // rows a lane (R) and lanes a column (P): the smallest P R >= dk of this table
-      static const int RP[8][3] = {{8, 8, 1}, {16, 8, 2}, {32, 8, 4}, {64, 8, 8}, {128, 16, 8}, {256, 16, 16}, {512, 16, 32}, {1024, 32, 32}};
-      int R = 32, P = 32;
-      for (int i = 7; i >= 0; i--) if (lc.dim <= RP[i][0]) { R = RP[i][1]; P = RP[i][2]; }
+      int R, P;
+      recur_shape(lc.dim, &R, &P);
       dim3 grid(b.E * lc.heads, (lc.vdim + 31) / 32);
-      float* st = m->delta_state + l.delta_off;
       // tokens per staged tile: two tiles of `per` floats a token within ~36 KB of shared memory
       const int per = 2 * P * (R + 4) + 36, TB = std::max(1, std::min(16, 4500 / per));
       const size_t dsm = (size_t)2 * TB * per * 4;
@@ -560,7 +784,34 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
 #undef DR
       PH(DN_SEQ_PH_DELTA_OUT);
       CK(launch(k_delta_out<T>, dim3(N, lc.heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_OUT_NORM), lc.heads, lc.vdim,
-                c.eps, (T*)m->mo));
+                c.eps, (T*)m->mo, 0));
+    } else {     // DN_MIX_WKV: token-shifted inputs, projections of each, the recurrence read with a bonus
+      PH(DN_SEQ_PH_PROJ);
+      ShiftMu<T> mu{{w(DN_SQ_MU_R), w(DN_SQ_MU_K), w(DN_SQ_MU_V), w(DN_SQ_MU_G), w(DN_SQ_MU_W)}, 5};
+      const size_t xs_ = (size_t)m->MB * W;
+      T* xm = (T*)m->xm;
+      CK(launch(k_shift_mix<T>, dim3(N), dim3(256), 0, s, (const T*)m->h, b, W, mu, (const T*)cst, m->conv_stride, xm, xs_));
+      CK(launch(k_shift_carry<T>, dim3((W + 255) / 256, b.E), dim3(256), 0, s, (const T*)m->h, b, W, cst, m->conv_stride));
+      if (few) {
+        add(xm, DN_SQ_Q, m->uq, l.Cq, 0); add(xm + xs_, DN_SQ_K, m->uk, l.Ck, 0); add(xm + 2 * xs_, DN_SQ_V, m->uv, l.Cv, 0);
+        add(xm + 3 * xs_, DN_SQ_G, m->gt, l.Co, 0);
+        CK(run_segs());
+      } else {
+        CK(linear<T>(m, s, xm, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &m->x_xm[0]}));
+        CK(linear<T>(m, s, xm + xs_, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_K), nullptr, &m->x_xm[1]}));
+        CK(linear<T>(m, s, xm + 2 * xs_, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_xm[2]}));
+        CK(linear<T>(m, s, xm + 3 * xs_, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0, LinMaps{wm(DN_SQ_G), nullptr, &m->x_xm[3]}));
+      }
+      CK(linear<T>(m, s, xm + 4 * xs_, l.w[DN_SQ_DECAY1], nullptr, m->lr, N, lc.rank, W, false, ACT_TANH, LinMaps{nullptr, nullptr, nullptr}));
+      CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_DECAY2], nullptr, m->dz, N, l.Cq, lc.rank, true, 0, LinMaps{wm(DN_SQ_DECAY2), nullptr, &l.x_lr}));
+      PH(DN_SEQ_PH_RECUR_PREP);
+      CK(launch(k_decay_prep<T>, dim3(N), dim3(256), 0, s, RECUR_BONUS, N, l.Cq, l.Cv, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_DECAY_B),
+                1.f, 1.f, m->qn, m->kn, m->vv, m->dz));
+      PH(DN_SEQ_PH_RECUR);
+      { const int rc = decay_rule(m, b, RECUR_BONUS, lc.heads, lc.dim, lc.vdim, l.w[DN_SQ_BONUS], st, s); if (rc != DN_OK) return rc; }
+      PH(DN_SEQ_PH_RECUR_OUT);
+      CK(launch(k_delta_out<T>, dim3(N, lc.heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_OUT_NORM), lc.heads, lc.vdim,
+                c.eps, (T*)m->mo, lc.vdim));
     }
     if (lc.conv > 1) {
       PH(DN_SEQ_PH_CARRY);
@@ -569,27 +820,65 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     }
     PH(DN_SEQ_PH_OUT_PROJ);
     CK(linear<T>(m, s, (const T*)m->mo, l.w[DN_SQ_O], nullptr, m->y, N, W, l.Co, true, 0, LinMaps{wm(DN_SQ_O), nullptr, &l.x_mo}));
+    if (lc.mixer == DN_MIX_PARALLEL) {     // the linear-attention half, on the same input; its scratch is free again
+      PH(DN_SEQ_PH_PROJ);
+      if (few) {
+        memset(&sg, 0, sizeof(sg));
+        add(nullptr, DN_SQ_R_Q, m->uq, l.Rc, 0); add(nullptr, DN_SQ_R_K, m->uk, l.Rc, 0); add(nullptr, DN_SQ_R_V, m->uv, l.Rv, 0);
+        add(nullptr, DN_SQ_R_G, m->gt, l.Rv, 0); add(nullptr, DN_SQ_DECAY1, m->lr, lc.rank, 0);
+        CK(run_segs());
+      } else {
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_Q], nullptr, m->uq, N, l.Rc, W, false, 0, LinMaps{wm(DN_SQ_R_Q), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_K], nullptr, m->uk, N, l.Rc, W, false, 0, LinMaps{wm(DN_SQ_R_K), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_V], nullptr, m->uv, N, l.Rv, W, false, 0, LinMaps{wm(DN_SQ_R_V), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_G], nullptr, m->gt, N, l.Rv, W, false, 0, LinMaps{wm(DN_SQ_R_G), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_DECAY1], nullptr, m->lr, N, lc.rank, W, false, 0, LinMaps{wm(DN_SQ_DECAY1), nullptr, &m->x_h}));
+      }
+      CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_DECAY2], nullptr, m->dz, N, l.Rc, lc.rank, true, 0, LinMaps{wm(DN_SQ_DECAY2), nullptr, &l.x_lr}));
+      PH(DN_SEQ_PH_RECUR_PREP);
+      CK(launch(k_decay_prep<T>, dim3(N), dim3(256), 0, s, RECUR_AFTER, N, l.Rc, l.Rv, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_DECAY_B),
+                1.f / sqrtf((float)lc.r_dim), lc.tau, m->qn, m->kn, m->vv, m->dz));
+      PH(DN_SEQ_PH_RECUR);
+      { const int rc = decay_rule(m, b, RECUR_AFTER, lc.r_heads, lc.r_dim, lc.r_vdim, nullptr, st, s); if (rc != DN_OK) return rc; }
+      PH(DN_SEQ_PH_RECUR_OUT);
+      CK(launch(k_delta_out<T>, dim3(N, lc.r_heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_R_NORM), lc.r_heads, lc.r_vdim,
+                c.eps, (T*)m->mo, 0));
+      PH(DN_SEQ_PH_OUT_PROJ);
+      CK(linear<T>(m, s, (const T*)m->mo, l.w[DN_SQ_R_O], nullptr, m->y2, N, W, l.Rv, true, 0, LinMaps{wm(DN_SQ_R_O), nullptr, &l.x_mo_r}));
+      ja = lc.left_scale; jb = lc.right_scale; jy2 = m->y2;
+    }
     PH(DN_SEQ_PH_WRITE_BACK);
-    CK(write_back(w(DN_SQ_HC1_MIX), w(DN_SQ_HC1_OUT)));
+    CK(join(l, DN_SQ_POST1, DN_SQ_HC1_MIX, DN_SQ_HC1_OUT, ja, jy2, jb));
     // ---- feed-forward sublayer
     if (lc.ff > 0) {
       PH(DN_SEQ_PH_NORM);
-      CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h));
-      PH(DN_SEQ_PH_FF_UP);
-      CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, 1, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));
-      PH(DN_SEQ_PH_FF_DOWN);
-      CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0, LinMaps{wm(DN_SQ_DOWN), nullptr, &l.x_act}));
-      PH(DN_SEQ_PH_WRITE_BACK);
-      CK(write_back(w(DN_SQ_HC2_MIX), w(DN_SQ_HC2_OUT)));
+      CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
+                w(DN_SQ_NORM2_B), dyt ? w(DN_SQ_NORM2_ALPHA) : (const T*)nullptr));
+      if (lc.mlp_kind == DN_MLP_MOE) {
+        const int rc = moe_ff<T>(m, l, N, s);
+        if (rc != DN_OK) return rc;
+        PH(DN_SEQ_PH_WRITE_BACK);
+        CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, lc.shared_ff > 0 ? (const float*)m->y2 : nullptr, 1.f));
+      } else {
+        PH(DN_SEQ_PH_FF_UP);
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, ACT_GEGLU, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));
+        PH(DN_SEQ_PH_FF_DOWN);
+        CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0, LinMaps{wm(DN_SQ_DOWN), nullptr, &l.x_act}));
+        PH(DN_SEQ_PH_WRITE_BACK);
+        CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, nullptr, 0.f));
+      }
     }
     PH(DN_SEQ_PH_OTHER);
-    if (trace) CK(launch(k_stream_sum, dim3(ew), dim3(256), 0, s, (const float*)m->xs, N, W, S1, trace + (size_t)li * N * W));
+    if (trace) CK(launch(k_stream_sum, dim3(ew), dim3(256), 0, s, (const float*)m->xs, N, W, S1, trace + (size_t)ri * N * W));
   }
   if (n_want > 0) {
     PH(DN_SEQ_PH_NORM);
-    CK(launch(k_read_norm<T>, dim3(n_want), nthr, nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, 1, 1, c.eps, want_dev, (T*)m->h));
+    CK(launch(k_read_norm<T>, dim3(n_want), nthr, nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, dyt ? 0 : 1, 1, c.eps, want_dev, (T*)m->h,
+              mwp(DN_SQ_FINAL_NORM_B), dyt ? mwp(DN_SQ_FINAL_NORM_ALPHA) : (const T*)nullptr));
     PH(DN_SEQ_PH_HEAD);
     CK(linear<T>(m, s, (const T*)m->h, m->head, nullptr, logits, n_want, c.vocab, W, true, 0, LinMaps{m->tm_head_ok ? &m->tm_head : nullptr, nullptr, &m->x_h}));
+    if (c.logit_softcap > 0.f)
+      CK(launch(k_softcap, dim3((unsigned)(((size_t)n_want * c.vocab + 255) / 256)), dim3(256), 0, s, logits, (size_t)n_want * c.vocab, c.logit_softcap));
   }
   PH(DN_SEQ_PH_OTHER);
 #undef PH
@@ -619,14 +908,37 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
   if (need > m->free_pages.size()) return fail(DN_ENOSPC, "cache pool exhausted: %zu pages needed, %zu free", need, m->free_pages.size());
   for (int i = 0; i < n_want; i++) if (want[i] < 0 || want[i] >= N) return fail(DN_EINVAL, "wanted row %d out of range", want[i]);
   if (!m->embed || !m->final_norm || !m->head) return fail(DN_ENOENT, "embedding / final norm / head are not bound");
+  const bool dyt = m->cfg.norm_kind == DN_NORM_DYT;
+  auto mhas = [&](int k) { return m->mw[k - DN_SQ_EMBED] != nullptr; };
+  if (dyt && (!mhas(DN_SQ_FINAL_NORM_B) || !mhas(DN_SQ_FINAL_NORM_ALPHA))) return fail(DN_ENOENT, "bias / alpha of the final norm are not bound");
+  if (m->cfg.embed_norm && (!mhas(DN_SQ_EMBED_NORM) || !mhas(DN_SQ_EMBED_NORM_B) || !mhas(DN_SQ_EMBED_NORM_ALPHA))) return fail(DN_ENOENT, "the embedding's norm is not bound");
+  if (m->cfg.loop_times > 0 && !mhas(DN_SQ_LOOP_IN)) return fail(DN_ENOENT, "the loop's input matrix is not bound");
   for (int i = 0; i < m->cfg.n_layers; i++) {
     const SeqLayer& l = m->L[i];
     auto has = [&](int k) { return l.w[k] != nullptr; };
-    bool ok = has(DN_SQ_NORM1) && has(DN_SQ_Q) && has(DN_SQ_O) && (l.c.ff == 0 || (has(DN_SQ_NORM2) && has(DN_SQ_GATE) && has(DN_SQ_UP) && has(DN_SQ_DOWN)));
+    const int mx = l.c.mixer;
+    const bool moe = l.c.mlp_kind == DN_MLP_MOE;
+    bool ok = has(DN_SQ_NORM1) && has(DN_SQ_Q) && has(DN_SQ_O) && (l.c.ff == 0 || has(DN_SQ_NORM2));
+    if (l.c.ff > 0 && !moe) ok = ok && has(DN_SQ_GATE) && has(DN_SQ_UP) && has(DN_SQ_DOWN);
+    if (l.c.ff > 0 && moe) {
+      ok = ok && has(DN_SQ_ROUTER) && (l.c.shared_ff == 0 || (has(DN_SQ_SH_GATE) && has(DN_SQ_SH_UP) && has(DN_SQ_SH_DOWN)));
+      for (const void* p : l.etab_h) ok = ok && p != nullptr;
+    }
+    if (dyt) ok = ok && has(DN_SQ_NORM1_B) && has(DN_SQ_NORM1_ALPHA) && (l.c.ff == 0 || (has(DN_SQ_NORM2_B) && has(DN_SQ_NORM2_ALPHA)));
+    if (m->cfg.post_norm) ok = ok && has(DN_SQ_POST1) && has(DN_SQ_POST1_B) && has(DN_SQ_POST1_ALPHA) &&
+                               (l.c.ff == 0 || (has(DN_SQ_POST2) && has(DN_SQ_POST2_B) && has(DN_SQ_POST2_ALPHA)));
     if (l.Ck) ok = ok && has(DN_SQ_K) && has(DN_SQ_V);
     if (l.c.conv > 0) ok = ok && has(DN_SQ_Q_CONV) && (!l.Ck || (has(DN_SQ_K_CONV) && has(DN_SQ_V_CONV)));
-    if (l.c.mixer == DN_MIX_ATTENTION) ok = ok && has(DN_SQ_Q_NORM) && (!l.Ck || has(DN_SQ_K_NORM));
-    else ok = ok && has(DN_SQ_A) && has(DN_SQ_B) && has(DN_SQ_G) && has(DN_SQ_A_LOG) && has(DN_SQ_DT_BIAS) && has(DN_SQ_OUT_NORM);
+    if (mx == DN_MIX_ATTENTION || mx == DN_MIX_PARALLEL) {
+      if (l.c.qk_norm) ok = ok && has(DN_SQ_Q_NORM) && (!l.Ck || has(DN_SQ_K_NORM));
+      if (l.c.sink) ok = ok && has(DN_SQ_SINK);
+      if (l.c.out_gate) ok = ok && has(DN_SQ_HEAD_GATE);
+    }
+    if (mx == DN_MIX_DELTA) ok = ok && has(DN_SQ_A) && has(DN_SQ_B) && has(DN_SQ_G) && has(DN_SQ_A_LOG) && has(DN_SQ_DT_BIAS) && has(DN_SQ_OUT_NORM);
+    if (mx == DN_MIX_PARALLEL) ok = ok && has(DN_SQ_R_Q) && has(DN_SQ_R_K) && has(DN_SQ_R_V) && has(DN_SQ_R_G) && has(DN_SQ_R_O) && has(DN_SQ_R_NORM) &&
+                                    has(DN_SQ_DECAY1) && has(DN_SQ_DECAY2) && has(DN_SQ_DECAY_B);
+    if (mx == DN_MIX_WKV) ok = ok && has(DN_SQ_G) && has(DN_SQ_OUT_NORM) && has(DN_SQ_DECAY1) && has(DN_SQ_DECAY2) && has(DN_SQ_DECAY_B) && has(DN_SQ_BONUS) &&
+                               has(DN_SQ_MU_R) && has(DN_SQ_MU_K) && has(DN_SQ_MU_V) && has(DN_SQ_MU_G) && has(DN_SQ_MU_W);
     if (m->cfg.streams > 0) ok = ok && has(DN_SQ_HC1_IN) && has(DN_SQ_HC1_OUT) && has(DN_SQ_HC1_MIX) &&
                                  (l.c.ff == 0 || (has(DN_SQ_HC2_IN) && has(DN_SQ_HC2_OUT) && has(DN_SQ_HC2_MIX)));
     if (!ok) return fail(DN_ENOENT, "layer %d: not every tensor of the layer is bound", i);

@@ -15,6 +15,9 @@
 //   * paged softmax attention with a causal mask restricted to the query's own block of `chunk` positions
 //     (chunk = 0: plain causal), GQA, separate key and value widths, optional reuse of another layer's pages
 //   * gated delta rule: per head a [dk, dv] fp32 state with decay, delta-rule write and read-out
+//   * dynamic-tanh norm (no statistics), capped scores, a sink term in the softmax denominator, per-head output gates
+//   * (dn_seq_recur.cuh) decayed outer-product recurrences with a decay per key channel, token-shift mixing
+//   * (dn_seq_moe.cuh) routed clamped-GLU experts
 // T is the storage type of weights and activations (bf16 or float); sums, norms, scores, positions, gates and
 // states are fp32 in both.
 #pragma once
@@ -65,6 +68,27 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+// clamped GLU: g = min(gate, limit), u = clamp(up, -limit, limit); g sigmoid(1.702 g) (u + 1)
+__device__ __forceinline__ float clamped_glu_f(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoid_f(1.702f * g) * (u + 1.f);
+}
+// activation of a product's epilogue: 0 none; 1 gelu_tanh(a) * b; 2 tanh(a); 3 clamped GLU of (a, b) with `lim`
+constexpr int ACT_NONE = 0, ACT_GEGLU = 1, ACT_TANH = 2, ACT_CGLU = 3;
+__device__ __forceinline__ bool act_two(int act) { return act == ACT_GEGLU || act == ACT_CGLU; }
+__device__ __forceinline__ float act_apply(int act, float a, float b, float lim) {
+  if (act == ACT_GEGLU) return gelu_tanh_f(a) * b;
+  if (act == ACT_TANH) return tanhf(a);
+  if (act == ACT_CGLU) return clamped_glu_f(a, b, lim);
+  return a;
+}
+// dynamic tanh: tanh(alpha x) w + b
+template <class T>
+__device__ __forceinline__ float dyt_f(float x, float alpha, const T* __restrict__ w, const T* __restrict__ b, int c) {
+  return tanhf(alpha * x) * ldf(w + c) + ldf(b + c);
+}
 
 // the batch of one step, all device pointers
 struct Batch {
@@ -82,13 +106,18 @@ struct Batch {
 
 // ---------------------------------------------------------------------------------------------------------------
 // embedding -> residual streams
+// nalpha != null: the embedding is dynamic-tanh normed; x0 != null: it is also kept aside (the loop's injection reads it)
 template <class T>
-__global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W, int S1, float* __restrict__ xs) {
+__global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W, int S1, float* __restrict__ xs, const T* __restrict__ nw,
+                        const T* __restrict__ nb, const T* __restrict__ nalpha, float* __restrict__ x0) {
   const int n = blockIdx.x;
   const size_t row = (size_t)b.tok[n] * W;
+  const float alpha = nalpha ? ldf(nalpha) : 0.f;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    const float v = ldf(embed + row + c) * scale;
+    float v = ldf(embed + row + c) * scale;
+    if (nalpha) v = dyt_f(v, alpha, nw, nb, c);
     for (int s = 0; s < S1; s++) xs[((size_t)s * b.N + n) * W + c] = v;
+    if (x0) x0[(size_t)n * W + c] = v;
   }
 }
 
@@ -97,7 +126,8 @@ __global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W
 // ascending order and the block adds the partials by index, so the result depends on W and the block size only.
 template <class T>
 __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, const T* __restrict__ hc_in, const T* __restrict__ nw,
-                            int one_plus, int sum_all, float eps, const int32_t* __restrict__ rows, T* __restrict__ h) {
+                            int one_plus, int sum_all, float eps, const int32_t* __restrict__ rows, T* __restrict__ h,
+                            const T* __restrict__ nb, const T* __restrict__ nalpha) {
   extern __shared__ __align__(16) float sm[];
   float* u = sm;            // [W]
   float* red = sm + W;      // [33]
@@ -123,6 +153,12 @@ __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, c
       u[c] = a;
       ss += a * a;
     }
+  }
+  if (nalpha) {        // dynamic tanh: no statistics of the row enter
+    __syncthreads();
+    const float alpha = ldf(nalpha);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(h + (size_t)r * W + c, dyt_f(u[c], alpha, nw, nb, c));
+    return;
   }
   ss = block_sum(ss, red);
   const float rinv = 1.f / sqrtf(ss / (float)W + eps);
@@ -180,6 +216,48 @@ __global__ void k_write_back(float* __restrict__ xs, int N, int W, int S, const 
   }
 }
 
+// a sublayer's output normed again (dynamic tanh) before it joins the plain residual:
+//   x <- x + dyt(a y + b y2)        (y2 optional: two branches of a mixer, or routed + shared experts)
+template <class T>
+__global__ void k_dyt_add(float* __restrict__ x, size_t NW, int W, const float* __restrict__ y, float a, const float* __restrict__ y2, float b,
+                          const T* __restrict__ nw, const T* __restrict__ nb, const T* __restrict__ nalpha) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= NW) return;
+  const int c = (int)(i % W);
+  float v = a * y[i];
+  if (y2) v += b * y2[i];
+  x[i] += dyt_f(v, ldf(nalpha), nw, nb, c);
+}
+// the same, in place, for models with residual streams (the write-back follows): y <- dyt(a y + b y2)
+template <class T>
+__global__ void k_dyt_inplace(float* __restrict__ y, size_t NW, int W, float a, const float* __restrict__ y2, float b, const T* __restrict__ nw,
+                              const T* __restrict__ nb, const T* __restrict__ nalpha) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= NW) return;
+  float v = a * y[i];
+  if (y2) v += b * y2[i];
+  y[i] = dyt_f(v, ldf(nalpha), nw, nb, (int)(i % W));
+}
+// y <- a y + b y2 (two branches of a mixer joined without a norm)
+__global__ void k_axpby(float* __restrict__ y, size_t NW, float a, const float* __restrict__ y2, float b) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < NW) y[i] = a * y[i] + b * y2[i];
+}
+// the loop's injection operand: cat[n] = [T(x[n]); T(x0[n])]
+template <class T>
+__global__ void k_loop_cat(const float* __restrict__ x, const float* __restrict__ x0, int N, int W, T* __restrict__ cat) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)N * 2 * W) return;
+  const size_t n = i / (2 * W);
+  const int c = (int)(i % (2 * W));
+  stf(cat + i, c < W ? x[n * W + c] : x0[n * W + c - W]);
+}
+// logits <- cap tanh(logits / cap)
+__global__ void k_softcap(float* __restrict__ z, size_t n, float cap) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) z[i] = cap * tanhf(z[i] / cap);
+}
+
 // sum of the streams (inspection hook)
 __global__ void k_stream_sum(const float* __restrict__ xs, int N, int W, int S1, float* __restrict__ o) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -191,10 +269,11 @@ __global__ void k_stream_sum(const float* __restrict__ xs, int N, int W, int S1,
 
 // ---------------------------------------------------------------------------------------------------------------
 // Y[N, O] = X[N, K] W[O, K]^T, fp32 accumulation in ascending k; CUDA-core tiles (any N, O, K).
-// OUT32: write fp32 (residual-side outputs), else T.  act 0: none; 1: Y = gelu_tanh(X W^T) * (X W2^T).
+// OUT32: write fp32 (residual-side outputs), else T.  act: ACT_* (the two-operand ones read W2 as well).
 template <class T, bool OUT32>
 __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
-                                                void* __restrict__ Y, int N, int O, int K, int act) {
+                                                void* __restrict__ Y, int N, int O, int K, int act, float alim) {
+  const bool two = act_two(act);
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float Xs[BK][BM + 4], Ws[BK][BN + 4], Vs[BK][BN + 4];
   const int n0 = blockIdx.y * BM, o0 = blockIdx.x * BN;
@@ -209,7 +288,7 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
       const int r = e / BK, c = e % BK;
       Xs[c][r] = (n0 + r < N && k0 + c < K) ? ldf(X + (size_t)(n0 + r) * K + k0 + c) : 0.f;
       Ws[c][r] = (o0 + r < O && k0 + c < K) ? ldf(Wt + (size_t)(o0 + r) * K + k0 + c) : 0.f;
-      if (act) Vs[c][r] = (o0 + r < O && k0 + c < K) ? ldf(W2 + (size_t)(o0 + r) * K + k0 + c) : 0.f;
+      if (two) Vs[c][r] = (o0 + r < O && k0 + c < K) ? ldf(W2 + (size_t)(o0 + r) * K + k0 + c) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -223,7 +302,7 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
       for (int i = 0; i < 4; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
-      if (act) {
+      if (two) {
 #pragma unroll
         for (int j = 0; j < 4; j++) w[j] = Vs[k][tx * 4 + j];
 #pragma unroll
@@ -242,8 +321,7 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
     for (int j = 0; j < 4; j++) {
       const int o = o0 + tx * 4 + j;
       if (o >= O) continue;
-      float v = acc[i][j];
-      if (act) v = gelu_tanh_f(v) * acc2[i][j];
+      const float v = act_apply(act, acc[i][j], acc2[i][j], alim);
       if (OUT32) ((float*)Y)[(size_t)n * O + o] = v;
       else stf((T*)Y + (size_t)n * O + o, v);
     }
@@ -257,8 +335,9 @@ template <class T> struct Vec16 { static constexpr int n = 16 / sizeof(T); };
 // one warp, one output feature o of one product
 template <class T>
 __device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2, void* __restrict__ Y,
-                                           bool out32, int N, int O, int K, int act, int o) {
+                                           bool out32, int N, int O, int K, int actc, int o, float alim = 0.f) {
   constexpr int V = Vec16<T>::n;
+  const bool act = act_two(actc);
   const int lane = threadIdx.x & 31;
   float acc[8], acc2[8];
 #pragma unroll
@@ -301,7 +380,7 @@ __device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __r
   for (int i = 0; i < 8; i++) {
     if (i < N) {
       float v = warp_sum(acc[i]);
-      if (act) v = gelu_tanh_f(v) * warp_sum(acc2[i]);
+      v = act_apply(actc, v, act ? warp_sum(acc2[i]) : 0.f, alim);
       if (lane == 0) {
         if (out32) ((float*)Y)[(size_t)i * O + o] = v;
         else stf((T*)Y + (size_t)i * O + o, v);
@@ -311,15 +390,16 @@ __device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __r
 }
 template <class T, bool OUT32>
 __global__ void __launch_bounds__(256) k_linear_rows(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
-                                                     void* __restrict__ Y, int N, int O, int K, int act) {
+                                                     void* __restrict__ Y, int N, int O, int K, int act, float alim) {
   const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (o >= O) return;
-  linear_row<T>(X, Wt, W2, Y, OUT32, N, O, K, act, o);
+  linear_row<T>(X, Wt, W2, Y, OUT32, N, O, K, act, o, alim);
 }
 // several products of the same few rows in one launch (the projections of a mixer in a decode step): blocks are
 // dealt to the products in order, 8 output features each
-constexpr int MAX_SEGS = 6;
+constexpr int MAX_SEGS = 8;
 struct LinSegs {
+  const void* X[MAX_SEGS];   // null: the launch's common input
   const void* W[MAX_SEGS];
   void* Y[MAX_SEGS];
   int O[MAX_SEGS];
@@ -337,7 +417,7 @@ __global__ void __launch_bounds__(256) k_linear_rows_multi(const T* __restrict__
   if (i >= sg.n) return;
   const int o = blk * 8 + (threadIdx.x >> 5);
   if (o >= sg.O[i]) return;
-  linear_row<T>(X, (const T*)sg.W[i], (const T*)nullptr, sg.Y[i], sg.out32[i] != 0, N, sg.O[i], K, 0, o);
+  linear_row<T>(sg.X[i] ? (const T*)sg.X[i] : X, (const T*)sg.W[i], (const T*)nullptr, sg.Y[i], sg.out32[i] != 0, N, sg.O[i], K, 0, o);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -382,6 +462,7 @@ __global__ void k_conv_carry(CarrySrc<T> src, int taps, Batch b, T* __restrict__
 struct AttnPrep {
   int H, G, dk, dv, taps, rot;       // heads, kv heads, key dim, value dim, conv taps (0: none), rotated dims
   int own_kv;                        // 0: keys / values come from another layer's pages
+  int norm;                          // 0: q and k pass without the RMS norm
   float eps;
   const float* inv_freq;             // [rot/2]
 };
@@ -417,7 +498,7 @@ __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const
     }
     sk = block_sum(sk, red);
   }
-  const float rq = 1.f / sqrtf(sq / (float)Cq + a.eps), rk = 1.f / sqrtf(sk / (float)Ck + a.eps);
+  const float rq = a.norm ? 1.f / sqrtf(sq / (float)Cq + a.eps) : 1.f, rk = a.norm ? 1.f / sqrtf(sk / (float)Ck + a.eps) : 1.f;
   const int page = b.bt[(size_t)slot * b.max_pages + p / PAGE], prow = p % PAGE;
   const int halfk = a.dk / 2;
   // pairs (2i, 2i+1) of every head; odd dk leaves its last dim to the tail loop below
@@ -427,7 +508,8 @@ __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const
     const int head = isq ? hh : hh - a.H;
     const int c0 = head * a.dk + 2 * i;
     float x0, x1;
-    if (isq) { x0 = qs[c0] * rq * ldf(nq + c0); x1 = qs[c0 + 1] * rq * ldf(nq + c0 + 1); }
+    if (!a.norm) { x0 = isq ? qs[c0] : ks[c0]; x1 = isq ? qs[c0 + 1] : ks[c0 + 1]; }
+    else if (isq) { x0 = qs[c0] * rq * ldf(nq + c0); x1 = qs[c0 + 1] * rq * ldf(nq + c0 + 1); }
     else { x0 = ks[c0] * rk * ldf(nk + c0); x1 = ks[c0 + 1] * rk * ldf(nk + c0 + 1); }
     if (2 * i + 1 < a.rot) {
       const float ang = (float)p * a.inv_freq[i];
@@ -446,8 +528,8 @@ __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const
     for (int hh = threadIdx.x; hh < a.H + (a.own_kv ? a.G : 0); hh += blockDim.x) {
       const bool isq = hh < a.H;
       const int c = (isq ? hh : hh - a.H) * a.dk + a.dk - 1;
-      if (isq) stf(qout + (size_t)n * Cq + c, qs[c] * rq * ldf(nq + c));
-      else stf(kpool + ((size_t)page * PAGE + prow) * Ck + c, ks[c] * rk * ldf(nk + c));
+      if (isq) stf(qout + (size_t)n * Cq + c, a.norm ? qs[c] * rq * ldf(nq + c) : qs[c]);
+      else stf(kpool + ((size_t)page * PAGE + prow) * Ck + c, a.norm ? ks[c] * rk * ldf(nk + c) : ks[c]);
     }
   }
   if (a.own_kv) {
@@ -463,6 +545,14 @@ __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const
 // merges the warps' partials in warp order -- a row's result depends on its own position only.  A lane scores
 // one key of the tile (its K row in 16-byte loads when the head size allows) and owns ceil(dv / 32) adjacent
 // output dims.
+// Extras of the scores (all optional): softcap > 0 caps a scaled score to softcap tanh(score / softcap); sink (one
+// number per head) adds exp(sink_h) to the softmax denominator -- a key without a value, neither scaled nor capped;
+// gate ([N, H] fp32 pre-activations) multiplies head h's output by sigmoid(gate[n, h]).
+struct AttnExtra {
+  float softcap;
+  const void* sink;
+  const float* gate;
+};
 constexpr int AT_WARPS = 8;
 template <class T>
 __device__ __forceinline__ void ld_vals(float (&v)[8], const T* p, int cnt, bool vec) {
@@ -489,7 +579,7 @@ __device__ __forceinline__ void ld_vals(float (&v)[8], const T* p, int cnt, bool
 template <class T>
 __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __restrict__ q, const T* __restrict__ kpool,
                                                         const T* __restrict__ vpool, int H, int G, int dk, int dv, int chunk, float scale,
-                                                        T* __restrict__ out) {
+                                                        AttnExtra ex, T* __restrict__ out) {
   extern __shared__ __align__(16) float sm[];
   constexpr int V = 16 / (int)sizeof(T);
   const int VPL = (dv + 31) / 32, dvp = VPL * 32;
@@ -525,6 +615,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
         for (int d = 0; d < dk; d++) d0 = fmaf(qs[d], ldf(kr + d), d0);
       }
       s = d0 * scale;
+      if (ex.softcap > 0.f) s = ex.softcap * tanhf(s / ex.softcap);
     }
     const float mn = fmaxf(m, warp_max(s));
     const float corr = expf(m - mn);      // exp(-inf) = 0 on the warp's first tile
@@ -551,17 +642,19 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   for (int i = 0; i < 8; i++)
     if (i < VPL) mine[2 + lane * VPL + i] = acc[i];
   __syncthreads();
+  const float snk = ex.sink ? ldf((const T*)ex.sink + h) : -INFINITY;
+  const float og = ex.gate ? sigmoid_f(ex.gate[(size_t)n * H + h]) : 1.f;
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
-    float M = -INFINITY;
+    float M = snk;
     for (int w = 0; w < AT_WARPS; w++) M = fmaxf(M, part[(size_t)w * (2 + dvp)]);
-    float L = 0.f, a = 0.f;
+    float L = ex.sink ? expf(snk - M) : 0.f, a = 0.f;
     for (int w = 0; w < AT_WARPS; w++) {
       const float* pw = part + (size_t)w * (2 + dvp);
       const float f = expf(pw[0] - M);     // a warp that saw no tile has maximum -inf and weight 0
       L += pw[1] * f;
       a += pw[2 + d] * f;
     }
-    stf(out + ((size_t)n * H + h) * dv + d, a / L);
+    stf(out + ((size_t)n * H + h) * dv + d, a / L * og);
   }
 }
 
@@ -606,7 +699,7 @@ constexpr int AT_ROWS = 64;      // query rows of a block, and keys of a tile (=
 template <int DKP, int DVP>
 __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restrict__ q, const bf16* __restrict__ kpool,
                                                     const bf16* __restrict__ vpool, int H, int G, int dk, int dv, int chunk, float scale,
-                                                    bf16* __restrict__ out) {
+                                                    AttnExtra ex, bf16* __restrict__ out) {
   static_assert(PAGE == AT_ROWS, "a key tile is one page");
   constexpr int LQ = DKP + 8, LV = DVP + 8;
   extern __shared__ __align__(16) unsigned char smraw[];
@@ -671,8 +764,10 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
 #pragma unroll
       for (int i = 0; i < 2; i++) {
         const int key = j0 + j * 8 + (lane & 3) * 2 + i;
-        sc[j][i] = (key <= p0 && key >= lo0) ? sc[j][i] * scale : -INFINITY;
-        sc[j][2 + i] = (key <= p1 && key >= lo1) ? sc[j][2 + i] * scale : -INFINITY;
+        float a0 = sc[j][i] * scale, a1 = sc[j][2 + i] * scale;
+        if (ex.softcap > 0.f) { a0 = ex.softcap * tanhf(a0 / ex.softcap); a1 = ex.softcap * tanhf(a1 / ex.softcap); }
+        sc[j][i] = (key <= p0 && key >= lo0) ? a0 : -INFINITY;
+        sc[j][2 + i] = (key <= p1 && key >= lo1) ? a1 : -INFINITY;
         mx0 = fmaxf(mx0, sc[j][i]);
         mx1 = fmaxf(mx1, sc[j][2 + i]);
       }
@@ -722,7 +817,19 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
     }
   }
   if (!warp_live) return;
-  const float i0 = p0 >= 0 ? 1.f / l0 : 0.f, i1 = p1 >= 0 ? 1.f / l1 : 0.f;
+  if (ex.sink) {       // one more term of the denominator, with no value: fold it in as a last key
+    const float snk = __bfloat162float(((const bf16*)ex.sink)[h]);
+    const float n0 = fmaxf(m0, snk), n1 = fmaxf(m1, snk);
+    const float c0 = expf(m0 - n0), c1 = expf(m1 - n1);
+    l0 = l0 * c0 + expf(snk - n0); l1 = l1 * c1 + expf(snk - n1);
+#pragma unroll
+    for (int j = 0; j < DVP / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+  }
+  float i0 = p0 >= 0 ? 1.f / l0 : 0.f, i1 = p1 >= 0 ? 1.f / l1 : 0.f;
+  if (ex.gate) {
+    if (p0 >= 0) i0 *= sigmoid_f(ex.gate[(size_t)(s0 + r0) * H + h]);
+    if (p1 >= 0) i1 *= sigmoid_f(ex.gate[(size_t)(s0 + r1) * H + h]);
+  }
 #pragma unroll
   for (int j = 0; j < DVP / 8; j++) {
     const int d = j * 8 + (lane & 3) * 2;
@@ -888,16 +995,17 @@ __global__ void __launch_bounds__(32 * P) k_delta_rule(Batch b, int H, int G, in
 }
 
 // read-out of the recurrence: per head o / rms(o) * w * silu(gate) -> T.  One warp per (token, head).
+// wstride: 0 when the heads share one weight [dv], dv when every head has its own ([H, dv])
 template <class T>
 __global__ void __launch_bounds__(32) k_delta_out(const float* __restrict__ o, const T* __restrict__ gate, const T* __restrict__ nw, int H,
-                                                  int dv, float eps, T* __restrict__ out) {
+                                                  int dv, float eps, T* __restrict__ out, int wstride) {
   const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
   const size_t base = ((size_t)n * H + h) * dv;
   float ss = 0.f;
   for (int d = lane; d < dv; d += 32) ss += o[base + d] * o[base + d];
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)dv + eps);
-  for (int d = lane; d < dv; d += 32) stf(out + base + d, o[base + d] * r * ldf(nw + d) * silu_f(ldf(gate + base + d)));
+  for (int d = lane; d < dv; d += 32) stf(out + base + d, o[base + d] * r * ldf(nw + (size_t)h * wstride + d) * silu_f(ldf(gate + base + d)));
 }
 
 }  // namespace dnseq

@@ -1,0 +1,184 @@
+// dn_seq_moe.cuh -- routed feed-forward of the batched sequence-mixer path (libdnet_b200_seq.so).
+//
+// A token's router logits z = W_r h + b_r are fp32; its `top` largest pick the experts, the softmax over those
+// logits alone weighs them.  An expert is a clamped GLU: g = min(W_g h, limit), u = clamp(W_u h, -limit, limit),
+// y = W_d (g sigmoid(1.702 g) (u + 1)).  The (token, choice) pairs P = N top are the rows of the expert products:
+//   * a few tokens (decode): pair p is row p; one warp per output feature streams the chosen expert's weight row
+//   * a prompt portion: k_moe_plan sorts the pairs by expert into 64-row tiles (a tile never spans two experts)
+//     and the tile kernels gather the tokens' rows; k_moe_combine adds a token's pairs in the order of its choices
+// so that a token's result does not depend on what else is in the step.
+#pragma once
+#include "dn_seq_kernels.cuh"
+
+namespace dnseq {
+
+// one block per token: logits, top-k (ties: the lower index), softmax over the chosen; pos[p] = p
+template <class T>
+__global__ void __launch_bounds__(128) k_router(const T* __restrict__ h, const T* __restrict__ Wr, const T* __restrict__ br, int W, int E,
+                                                int top, int32_t* __restrict__ idx, float* __restrict__ wt, int32_t* __restrict__ pos) {
+  extern __shared__ float zl[];      // [E]
+  const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const T* x = h + (size_t)n * W;
+  for (int e = warp; e < E; e += nw) {
+    const T* wr = Wr + (size_t)e * W;
+    float a = 0.f;
+    for (int c = lane; c < W; c += 32) a = fmaf(ldf(x + c), ldf(wr + c), a);
+    a = warp_sum(a);
+    if (lane == 0) zl[e] = a + (br ? ldf(br + e) : 0.f);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float best[16];
+    int32_t* id = idx + (size_t)n * top;
+    for (int j = 0; j < top; j++) {
+      int arg = -1;
+      float m = -INFINITY;
+      for (int e = 0; e < E; e++) {
+        bool taken = false;
+        for (int i = 0; i < j; i++) taken = taken || id[i] == e;
+        if (!taken && (arg < 0 || zl[e] > m)) { m = zl[e]; arg = e; }
+      }
+      id[j] = arg;
+      best[j] = m;
+    }
+    float s = 0.f;
+    const float zmax = best[0];
+    for (int j = 0; j < top; j++) { best[j] = expf(best[j] - zmax); s += best[j]; }
+    for (int j = 0; j < top; j++) {
+      wt[(size_t)n * top + j] = best[j] / s;
+      pos[(size_t)n * top + j] = n * top + j;
+    }
+  }
+}
+
+// pairs sorted by expert: pos[p] = row of pair p, row_tok[row] = its token, and the table of 64-row tiles
+struct MoePlan {
+  int32_t* pos;        // [P]
+  int32_t* row_tok;    // [P]
+  int32_t* tile_e;     // [max tiles]
+  int32_t* tile_r0;
+  int32_t* tile_rows;
+  int32_t* n_tiles;    // [1]
+};
+constexpr int MOE_ROWS = 64;
+__global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ idx, int P, int top, int E, MoePlan pl) {
+  extern __shared__ int32_t cnt[];      // [E] counts, [E + 1] offsets
+  int32_t* off = cnt + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) pl.pos[p] = atomicAdd(&cnt[idx[p]], 1);     // rank among its expert's pairs
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int a = 0, t = 0;
+    for (int e = 0; e < E; e++) {
+      off[e] = a;
+      for (int r = 0; r < cnt[e]; r += MOE_ROWS, t++) {
+        pl.tile_e[t] = e;
+        pl.tile_r0[t] = a + r;
+        pl.tile_rows[t] = min(MOE_ROWS, cnt[e] - r);
+      }
+      a += cnt[e];
+    }
+    *pl.n_tiles = t;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int row = off[idx[p]] + pl.pos[p];
+    pl.pos[p] = row;
+    pl.row_tok[row] = p / top;
+  }
+}
+
+// expert tables of a layer: etab[0..E) gate, [E..2E) up, [2E..3E) down
+// tile products on the CUDA cores (any sizes; fp32 accumulation in ascending k).  UP: act[row] = cglu(x W_g^T, x W_u^T)
+// with x the row's token gathered from X [N, K]; DOWN: out[row] = act[row] W_d^T, fp32.
+template <class T, bool UP>
+__global__ void __launch_bounds__(256) k_moe_tiles(const T* __restrict__ X, const void* const* __restrict__ etab, int E, MoePlan pl,
+                                                   void* __restrict__ Y, int O, int K, float limit) {
+  constexpr int BM = MOE_ROWS, BN = 64, BK = 16;
+  const int t = blockIdx.y;
+  if (t >= *pl.n_tiles) return;
+  __shared__ float Xs[BK][BM + 4], Ws[BK][BN + 4], Vs[BK][BN + 4];
+  __shared__ int32_t src[BM];
+  const int e = pl.tile_e[t], r0 = pl.tile_r0[t], rows = pl.tile_rows[t];
+  const T* Wa = (const T*)etab[UP ? e : 2 * E + e];
+  const T* Wb = UP ? (const T*)etab[E + e] : nullptr;
+  for (int r = threadIdx.x; r < BM; r += 256) src[r] = r < rows ? (UP ? pl.row_tok[r0 + r] : r0 + r) : -1;
+  __syncthreads();
+  const int o0 = blockIdx.x * BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4], acc2[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = acc2[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int el = threadIdx.x; el < BM * BK; el += 256) {
+      const int r = el / BK, c = el % BK;
+      Xs[c][r] = (src[r] >= 0 && k0 + c < K) ? ldf(X + (size_t)src[r] * K + k0 + c) : 0.f;
+      Ws[c][r] = (o0 + r < O && k0 + c < K) ? ldf(Wa + (size_t)(o0 + r) * K + k0 + c) : 0.f;
+      if (UP) Vs[c][r] = (o0 + r < O && k0 + c < K) ? ldf(Wb + (size_t)(o0 + r) * K + k0 + c) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; k++) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = Xs[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) w[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+      if (UP) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) w[j] = Vs[k][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc2[i][j] = fmaf(a[i], w[j], acc2[i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int o = o0 + tx * 4 + j;
+      if (o >= O) continue;
+      if (UP) stf((T*)Y + (size_t)(r0 + r) * O + o, clamped_glu_f(acc[i][j], acc2[i][j], limit));
+      else ((float*)Y)[(size_t)(r0 + r) * O + o] = acc[i][j];
+    }
+  }
+}
+
+// a few tokens: pair p = blockIdx.y is row p; one warp per output feature of the pair's expert
+template <class T, bool UP>
+__global__ void __launch_bounds__(256) k_moe_rows(const T* __restrict__ X, const void* const* __restrict__ etab, int E, const int32_t* __restrict__ idx,
+                                                  int top, void* __restrict__ Y, int O, int K, float limit) {
+  const int p = blockIdx.y, e = idx[p];
+  const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (o >= O) return;
+  if (UP)
+    linear_row<T>(X + (size_t)(p / top) * K, (const T*)etab[e], (const T*)etab[E + e], (T*)Y + (size_t)p * O, false, 1, O, K, ACT_CGLU, o, limit);
+  else
+    linear_row<T>(X + (size_t)p * K, (const T*)etab[2 * E + e], (const T*)nullptr, (float*)Y + (size_t)p * O, true, 1, O, K, ACT_NONE, o, 0.f);
+}
+
+// y[n] = sum_j wt[n, j] out[pos[n, j]], the pairs of a token in the order of its choices
+__global__ void k_moe_combine(const float* __restrict__ eo, const float* __restrict__ wt, const int32_t* __restrict__ pos, int N, int W, int top,
+                              float* __restrict__ y) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)N * W) return;
+  const size_t n = i / W;
+  const int c = (int)(i % W);
+  float a = 0.f;
+  for (int j = 0; j < top; j++) a = fmaf(wt[n * top + j], eo[(size_t)pos[n * top + j] * W + c], a);
+  y[i] = a;
+}
+
+}  // namespace dnseq

@@ -45,8 +45,11 @@ def load_model(model_path, dtype: str = "bfloat16", *, max_tokens: int = 4096, m
     md = get_model_metadata(model_path)
     n = md.num_layers
     pages = max(1, (int(max_tokens) + PAGE - 1) // PAGE)
+    groups = (md.embed_tokens, md.norm, md.lm_head)
+    shapes = {f"l{li}.{suffix}": tuple(info.shape) for li, tensors in md.weight_info.items() for suffix, info in tensors.items()}
+    shapes.update({k[4:]: tuple(info.shape) for g in groups for k, info in g.items() if k.startswith("seq:")})
     model = get_ring_model(md.model_type, md.model_config, assigned_layers=list(range(n)), dtype=dtype, kv_pool_pages=pages,
-                           max_seqs=max_seqs, max_batch_tokens=max_batch_tokens)
+                           max_seqs=max_seqs, max_batch_tokens=max_batch_tokens, tensor_shapes=shapes)
     if not getattr(model, "batched_step", False):
         model.destroy()
         raise ValueError(f"model type {md.model_type!r} does not run batched steps; serve it through ShardRuntime")
@@ -65,6 +68,7 @@ def load_model(model_path, dtype: str = "bfloat16", *, max_tokens: int = 4096, m
     for name, group in (("embed", md.embed_tokens), ("final.norm", md.norm), ("head", md.lm_head)):
         if "weight" in group:
             items.append((name, dev(group["weight"])))
+        items += [(k[4:], dev(info)) for k, info in group.items() if k.startswith("seq:")]
     model.load_weights(items, strict=True)
     for f in mapped.values():
         f.close()

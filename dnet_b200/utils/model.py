@@ -29,6 +29,7 @@ NORM_RE = re.compile(r"^model\.norm\.(.+)$")
 # checkpoints of the layer-list families (core/models/seqmix.py): l<i>.<tensor>, embed, final.norm, head
 SEQ_LAYER_RE = re.compile(r"^l(\d+)\.(.+)$")
 SEQ_API = {"embed": "embed_tokens", "final.norm": "norm", "head": "lm_head"}
+SEQ_MODEL_RE = re.compile(r"^(embed|final|head|loop)\.(.+)$")
 
 
 def get_model_layer_name(layer_idx: int, name: str) -> str:
@@ -140,6 +141,8 @@ def _classify(details: Dict[str, TensorInfo], weight_info, embed_tokens, lm_head
             weight_info[int(layer_idx)][suffix] = val
         elif key in SEQ_API:
             {"embed_tokens": embed_tokens, "norm": norm, "lm_head": lm_head}[SEQ_API[key]]["weight"] = val
+        elif m := SEQ_MODEL_RE.match(key):      # other model tensors of a layer-list family, under their checkpoint names
+            {"embed": embed_tokens, "final": norm, "head": lm_head, "loop": norm}[m.group(1)]["seq:" + key] = val
         else:
             raise RuntimeError(f"Unexpected key {key}")
 

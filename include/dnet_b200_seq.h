@@ -1,7 +1,8 @@
 /*
  * dnet_b200_seq.h -- C ABI of libdnet_b200_seq.so: the batched step of decoder models whose layers are a
- * sequence mixer (chunk-masked softmax attention over a paged cache, or a gated delta-rule recurrence) plus an
- * optional gated feed-forward, tied together by S residual streams.
+ * sequence mixer (softmax attention over a paged cache -- block-masked, capped, with a sink and head gates --, a gated
+ * delta-rule recurrence, decayed outer-product recurrences, or attention beside one of those) plus an optional gated or
+ * routed feed-forward, tied together by S residual streams; a span of layers may run several times on the same weights.
  *
  * Same conventions as dnet_b200.h: plain C, opaque handles, 0 or a negative DN_E* code, dn_seq_last_error() for
  * the text, caller-owned streams and buffers, weights BORROWED by pointer.  One handle serves one compute thread.
@@ -24,6 +25,14 @@ extern "C" {
 
 #define DN_MIX_ATTENTION 0
 #define DN_MIX_DELTA 1
+#define DN_MIX_PARALLEL 2   /* softmax attention and a gated linear attention side by side on the same input */
+#define DN_MIX_WKV 3        /* token-shift mixing + a decayed outer-product state read with a bonus for the current token */
+
+#define DN_NORM_RMS 0       /* x / sqrt(mean(x^2) + eps) * w  (or 1 + w) */
+#define DN_NORM_DYT 1       /* tanh(alpha x) * w + b, elementwise */
+
+#define DN_MLP_DENSE 0      /* gelu_tanh(gate) * up -> down */
+#define DN_MLP_MOE 1        /* routed clamped-GLU experts (+ an optional shared one) */
 
 typedef struct dn_seq_model dn_seq_model;
 typedef void* dn_seq_stream;   /* cudaStream_t */
@@ -40,7 +49,23 @@ typedef struct dn_seq_layer_cfg {
   float rot_base;
   float scale;         /* attention: score scale */
   int32_t kv_from;     /* attention: layer whose pages hold this layer's keys and values (-1: its own) */
-  int32_t ff;          /* feed-forward width (0: the layer has no feed-forward) */
+  int32_t ff;          /* feed-forward width, of one expert for DN_MLP_MOE (0: the layer has no feed-forward) */
+  /* attention (also the attention half of DN_MIX_PARALLEL) */
+  int32_t qk_norm;     /* 1: RMS norm over the whole q and k projections with learned weights */
+  float softcap;       /* scores: cap * tanh(score / cap) after the scale (0: none) */
+  int32_t sink;        /* 1: the softmax denominator holds one more term exp(sink_h), a learned number per head */
+  int32_t out_gate;    /* 1: head h's output is multiplied by sigmoid(w_h . x), one gate per head */
+  /* the linear-attention half of DN_MIX_PARALLEL; DN_MIX_WKV uses heads / dim / vdim above and rank here */
+  int32_t r_heads, r_dim, r_vdim;
+  int32_t rank;        /* inner size of the two-step decay projection */
+  float tau;           /* DN_MIX_PARALLEL: decay = sigmoid(z)^(1/tau) */
+  float left_scale, right_scale;   /* DN_MIX_PARALLEL: result = left_scale * attention + right_scale * linear attention */
+  /* feed-forward */
+  int32_t mlp_kind;    /* DN_MLP_* */
+  int32_t experts, top;
+  float limit;         /* clamped GLU: gate <= limit, |up| <= limit */
+  int32_t shared_ff;   /* width of the shared expert (0: none) */
+  float shared_limit;
 } dn_seq_layer_cfg;
 
 typedef struct dn_seq_cfg {
@@ -52,6 +77,13 @@ typedef struct dn_seq_cfg {
   int32_t pool_pages;        /* 64-token pages in the cache pool */
   int32_t max_seqs;          /* state slots */
   int32_t max_batch_tokens;  /* most tokens one dn_seq_step may bring */
+  int32_t norm_kind;         /* DN_NORM_*: of every norm that spans the width */
+  int32_t post_norm;         /* 1: a sublayer's output is normed again before it joins the residual */
+  int32_t embed_norm;        /* 1: the embedding is normed */
+  float logit_softcap;       /* logits: cap * tanh(logit / cap) (0: none) */
+  /* layers loop_start .. loop_stop-1 run loop_times times in a row on the same weights, every pass with its own cache and
+   * state; before the first layer of each pass x <- W_in [x; x0] with x0 the embedding's output.  loop_times = 0: no loop */
+  int32_t loop_start, loop_stop, loop_times;
 } dn_seq_cfg;
 
 /* tensors of a layer (dn_seq_bind: layer >= 0) and of the model (layer = -1) */
@@ -61,9 +93,25 @@ enum {
   DN_SQ_A, DN_SQ_B, DN_SQ_G, DN_SQ_A_LOG, DN_SQ_DT_BIAS, DN_SQ_OUT_NORM,
   DN_SQ_GATE, DN_SQ_UP, DN_SQ_DOWN,
   DN_SQ_HC1_IN, DN_SQ_HC1_OUT, DN_SQ_HC1_MIX, DN_SQ_HC2_IN, DN_SQ_HC2_OUT, DN_SQ_HC2_MIX,
+  /* DN_NORM_DYT: bias and scalar alpha of the norms; the norms after a sublayer (post_norm) */
+  DN_SQ_NORM1_B, DN_SQ_NORM1_ALPHA, DN_SQ_NORM2_B, DN_SQ_NORM2_ALPHA,
+  DN_SQ_POST1, DN_SQ_POST1_B, DN_SQ_POST1_ALPHA, DN_SQ_POST2, DN_SQ_POST2_B, DN_SQ_POST2_ALPHA,
+  /* attention extras: per-head sink [H], per-head output gate [H, W] */
+  DN_SQ_SINK, DN_SQ_HEAD_GATE,
+  /* linear-attention half of DN_MIX_PARALLEL */
+  DN_SQ_R_Q, DN_SQ_R_K, DN_SQ_R_V, DN_SQ_R_G, DN_SQ_R_O, DN_SQ_R_NORM,
+  /* two-step decay projection [rank, W], [C, rank] and its bias [C] (DN_MIX_PARALLEL's right half, DN_MIX_WKV) */
+  DN_SQ_DECAY1, DN_SQ_DECAY2, DN_SQ_DECAY_B,
+  /* DN_MIX_WKV: token-shift coefficients of r, k, v, g, w [W] each; the current token's bonus [H, dk] */
+  DN_SQ_MU_R, DN_SQ_MU_K, DN_SQ_MU_V, DN_SQ_MU_G, DN_SQ_MU_W, DN_SQ_BONUS,
+  /* DN_MLP_MOE: router [E, W] and its bias [E]; the shared expert */
+  DN_SQ_ROUTER, DN_SQ_ROUTER_B, DN_SQ_SH_GATE, DN_SQ_SH_UP, DN_SQ_SH_DOWN,
   DN_SQ_COUNT,
-  DN_SQ_EMBED = 100, DN_SQ_FINAL_NORM, DN_SQ_HEAD
+  DN_SQ_EMBED = 100, DN_SQ_FINAL_NORM, DN_SQ_HEAD, DN_SQ_FINAL_NORM_B, DN_SQ_FINAL_NORM_ALPHA,
+  DN_SQ_EMBED_NORM, DN_SQ_EMBED_NORM_B, DN_SQ_EMBED_NORM_ALPHA, DN_SQ_LOOP_IN
 };
+/* matrices of a routed expert (dn_seq_bind_expert) */
+enum { DN_SQ_E_GATE = 0, DN_SQ_E_UP, DN_SQ_E_DOWN };
 
 int dn_seq_init(int device);
 const char* dn_seq_last_error(void);
@@ -72,6 +120,9 @@ int64_t dn_seq_launch_count(void);
 int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg* layers, dn_seq_model** out);
 int dn_seq_model_destroy(dn_seq_model* m);
 int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* dev_ptr);
+int dn_seq_bind_expert(dn_seq_model* m, int layer, int expert, int which, const void* dev_ptr);
+/* layer runs of a step: n_layers plus the repeated passes of the loop (rows of dn_seq_step's layer trace) */
+int dn_seq_layer_runs(dn_seq_model* m);
 
 /* sequences: open takes a free state slot (zeroed behind the work queued on s); close returns slot and pages */
 int dn_seq_open(dn_seq_model* m, dn_seq_stream s, int* slot_out);
@@ -82,7 +133,7 @@ int dn_seq_free_slots(dn_seq_model* m);
 
 /* One step: entry e brings counts[e] tokens (concatenated in tokens_host) of the sequence in slots[e]; the rows
  * want_host[0..n_want) of the concatenation get logits, written as fp32 [n_want, vocab] to logits_dev.
- * layer_trace_dev (optional): fp32 [n_layers, N, width], the residual (sum of the streams) after every layer.
+ * layer_trace_dev (optional): fp32 [layer runs, N, width], the residual (sum of the streams) after every layer run.
  * Asynchronous on s except for the staging of the previous step's arguments. */
 int dn_seq_step(dn_seq_model* m, int n_entries, const int32_t* slots, const int32_t* counts, const int32_t* tokens_host,
                 int n_want, const int32_t* want_host, float* logits_dev, float* layer_trace_dev, dn_seq_stream s);
@@ -97,7 +148,8 @@ int dn_seq_check(dn_seq_model* m, dn_seq_stream s);
 enum {
   DN_SEQ_PH_EMBED = 0, DN_SEQ_PH_NORM, DN_SEQ_PH_PROJ, DN_SEQ_PH_ATTN_PREP, DN_SEQ_PH_ATTN, DN_SEQ_PH_DELTA_PREP,
   DN_SEQ_PH_DELTA_RULE, DN_SEQ_PH_DELTA_OUT, DN_SEQ_PH_CARRY, DN_SEQ_PH_OUT_PROJ, DN_SEQ_PH_WRITE_BACK, DN_SEQ_PH_FF_UP,
-  DN_SEQ_PH_FF_DOWN, DN_SEQ_PH_HEAD, DN_SEQ_PH_OTHER, DN_SEQ_PH_COUNT
+  DN_SEQ_PH_FF_DOWN, DN_SEQ_PH_HEAD, DN_SEQ_PH_OTHER, DN_SEQ_PH_RECUR_PREP, DN_SEQ_PH_RECUR, DN_SEQ_PH_RECUR_OUT, DN_SEQ_PH_ROUTER,
+  DN_SEQ_PH_MOE_UP, DN_SEQ_PH_MOE_DOWN, DN_SEQ_PH_COUNT
 };
 int dn_seq_profile(dn_seq_model* m, int on);
 int dn_seq_profile_read(dn_seq_model* m, double* ms_out, int reset);

@@ -1,0 +1,447 @@
+"""The Filinex family (core/models/seqmix.py FilinexRingModel, shard/batching.py, libdnet_b200_seq) against the float64
+oracle (oracle/filinex_oracle.py): every mechanism alone with the residual after each layer run, then portions,
+batches, page and slot reuse, far keys and sinks made to stand out, long decoding and greedy generation through the
+batcher's token loop.  fp32 runs are held to 2e-4 of the logits' spread row by row.  bf16 runs are held to 4e-2 of
+the spread over all rows together, on weights whose routers are decisive (a choice of experts that bf16 rounding
+flips changes a row by far more than rounding does, and says nothing about the kernels)."""
+from __future__ import annotations
+
+import copy
+
+import pytest
+import torch
+
+from oracle import filinex_oracle as fo
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 2e-4, "bfloat16": 4e-2}
+
+MOE = {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 40, "limit": 1.25}, "shared": {"ff": 24, "limit": 0.75}}
+
+
+def par(mlp=None, left=None, right=None, **kw):
+    L = {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.3, "softcap": 8.0}
+    R = {"heads": 3, "dim": 16, "vdim": 8, "tau": 4.0}
+    L.update(left or {})
+    R.update(right or {})
+    mx = {"left": L, "right": R, "left_scale": 0.8, "right_scale": 1.5}
+    mx.update(kw)
+    return {"type": "parallel", "mixer": mx, "mlp": mlp}
+
+
+def wkv(mlp=None, **kw):
+    mx = {"heads": 3, "dim": 16}
+    mx.update(kw)
+    return {"type": "wkv", "mixer": mx, "mlp": mlp}
+
+
+def config(layers, loop=None, width=48, vocab=96, eps=1e-5, cap=9.0):
+    c = {"architecture": "Filinex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "logit_softcap": cap, "layers": layers}
+    if loop:
+        c["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return c
+
+
+FULL = config([par(MOE), wkv(MOE), wkv(None, heads=2, dim=8), par(MOE, left={"heads": 2, "kv_heads": 2, "dim": 8, "vdim": 8})], loop=(1, 3, 3))
+
+
+class Rig:
+    """a model + batcher on the GPU and the oracle's view of the same weights"""
+
+    def __init__(self, cfg, dtype="float32", seed=1, max_tokens=1024, max_seqs=4, max_batch_tokens=512, weights=None, rank=8):
+        from dnet_b200.shard.batching import SequenceBatcher, load_model
+        from dnet_b200.utils.model import HostDictSource
+
+        self.cfg, self.dtype = cfg, dtype
+        self.w = weights if weights is not None else fo.random_weights(cfg, seed, rank)
+        if dtype == "bfloat16":
+            self.w = decisive(self.w)
+        self.model = load_model(HostDictSource({k: v.to(torch.bfloat16) for k, v in self.w.items()}, cfg), dtype, max_tokens=max_tokens,
+                                max_seqs=max_seqs, max_batch_tokens=max_batch_tokens)
+        self.eng = SequenceBatcher(self.model)
+
+    def oracle(self, tokens, layers_out=None):
+        return fo.forward(self.cfg, self.w, tokens, layers_out)
+
+    def close(self):
+        self.eng.close()
+        self.model.destroy()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+
+def err(got: torch.Tensor, ref: torch.Tensor) -> float:
+    """worst row of: rms of the difference (mean removed) over the rms spread of the reference row"""
+    d = got.double().cpu() - ref.double()
+    d = d - d.mean(-1, keepdim=True)
+    r = ref.double() - ref.double().mean(-1, keepdim=True)
+    return float((d.pow(2).mean(-1).sqrt() / r.pow(2).mean(-1).sqrt().clamp_min(1e-9)).max())
+
+
+def err16(got: torch.Tensor, ref: torch.Tensor) -> float:
+    """rms of the difference (row means removed) over the rms spread of the reference, all rows together"""
+    d = got.double().cpu() - ref.double()
+    d = d - d.mean(-1, keepdim=True)
+    r = ref.double() - ref.double().mean(-1, keepdim=True)
+    return float(d.pow(2).mean().sqrt() / r.pow(2).mean().sqrt())
+
+
+def decisive(w):
+    """router biases far apart: the same experts win at every token, whatever the rounding"""
+    w = dict(w)
+    for k in w:
+        if k.endswith("mlp.router.b"):
+            n = w[k].numel()
+            w[k] = (4.0 * torch.arange(n).roll(n // 3)).to(torch.float32)
+    return w
+
+
+def toks(n, vocab=96, seed=0):
+    g = torch.Generator().manual_seed(2000 + seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def run_schedule(rig: Rig, tokens, cuts, rid="r"):
+    """feed tokens in portions of the given sizes (the rest one by one); logits of every position"""
+    out, at = [], 0
+    for c in list(cuts) + [1] * len(tokens):
+        if at >= len(tokens):
+            break
+        part = tokens[at:at + c]
+        out.append(rig.eng.step([(rid, part, list(range(len(part))))]))
+        at += len(part)
+    rig.eng.finish(rid)
+    return torch.cat(out)
+
+
+# -- each mechanism alone ---------------------------------------------------------------------------------------
+MECHANISMS = {
+    "wkv": config([wkv()]),
+    "wkv_one_head": config([wkv(heads=1, dim=32)]),
+    "wkv_dim_24": config([wkv(heads=2, dim=24)]),
+    "wkv_dim_72": config([wkv(heads=1, dim=72)]),
+    "wkv_dim_160": config([wkv(heads=1, dim=160)]),
+    "parallel": config([par()]),
+    "parallel_left_only": config([par(left_scale=1.0, right_scale=0.0)]),
+    "parallel_right_only": config([par(left_scale=0.0, right_scale=1.0)]),
+    "parallel_mha_equal_sizes": config([par(left={"heads": 2, "kv_heads": 2, "dim": 8, "vdim": 8}, right={"heads": 2, "dim": 8, "vdim": 8})]),
+    "parallel_one_head": config([par(left={"heads": 1, "kv_heads": 1, "dim": 32, "vdim": 40}, right={"heads": 1, "dim": 40, "vdim": 72})]),
+    "parallel_odd_sizes": config([par(left={"heads": 3, "kv_heads": 1, "dim": 10, "vdim": 7}, right={"heads": 2, "dim": 12, "vdim": 33})]),
+    "parallel_tight_cap": config([par(left={"softcap": 0.5, "scale": 2.0})]),
+    "parallel_tau_1": config([par(right={"tau": 1.0})]),
+    "moe": config([wkv(MOE)]),
+    "moe_top_1": config([wkv({**MOE, "router": {"experts": 4, "top": 1}})]),
+    "moe_all_experts": config([wkv({**MOE, "router": {"experts": 3, "top": 3}})]),
+    "moe_no_shared": config([par({**MOE, "shared": None})]),
+    "moe_many_experts": config([wkv({**MOE, "router": {"experts": 40, "top": 5}, "expert": {"ff": 8, "limit": 3.0}})]),
+    "loop_whole_model": config([wkv(MOE), par(MOE)], loop=(0, 2, 2)),
+    "loop_once": config([wkv(), par()], loop=(1, 2, 1)),
+    "loop_in_the_middle": config([par(), wkv(MOE), par(), wkv()], loop=(1, 3, 3)),
+    "no_loop": config([par(MOE), wkv(MOE)]),
+    "no_logit_cap": config([wkv()], cap=0.0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MECHANISMS))
+def test_mechanism_alone_fp32(name):
+    cfg = MECHANISMS[name]
+    t = toks(150, seed=3)
+    with Rig(cfg, "float32", seed=sum(map(ord, name))) as rig:
+        lo = []
+        ref = rig.oracle(t, lo)
+        got, trace = rig.eng.step([("a", t, list(range(len(t))))], layer_trace=True)
+        assert trace.shape[0] == len(lo)
+        for i, l in enumerate(lo):
+            assert err(trace[i], l) < TOL["float32"], f"{name}: residual after layer run {i}"
+        assert err(got, ref) < TOL["float32"]
+        assert err(run_schedule(rig, t[:40], [7, 2]), ref[:40]) < TOL["float32"], f"{name}: portions and decoding"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_model_whole_prompt(dtype):
+    t = toks(200, seed=5)
+    with Rig(FULL, dtype) as rig:
+        got = rig.eng.step([("a", t, list(range(len(t))))])
+        assert (err16 if dtype == "bfloat16" else err)(got, rig.oracle(t)) < TOL[dtype]
+
+
+def test_sizes_on_the_tensor_core_products():
+    """width and projection sizes in multiples of 64: bf16 prompt portions take the tcgen05 products and the MMA attention"""
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 128, "limit": 2.5}, "shared": {"ff": 192, "limit": 1.0}}
+    cfg = config([wkv(moe, heads=4, dim=32), par(moe, left={"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32}, right={"heads": 2, "dim": 32, "vdim": 64})],
+                 loop=(0, 2, 2), width=128, vocab=192)
+    t = toks(300, vocab=192, seed=6)
+    with Rig(cfg, "bfloat16", rank=64) as rig:
+        ref = rig.oracle(t)
+        assert err16(rig.eng.step([("a", t, list(range(len(t))))]), ref) < TOL["bfloat16"]
+        rig.eng.finish("a")
+        assert err16(run_schedule(rig, t, [130, 17, 64, 2, 70]), ref) < TOL["bfloat16"]
+
+
+# -- schedules ------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefill_against_token_by_token(dtype):
+    t = toks(90, seed=7)
+    with Rig(FULL, dtype) as rig:
+        ref = rig.oracle(t)
+        e = err16 if dtype == "bfloat16" else err
+        assert e(run_schedule(rig, t, []), ref) < TOL[dtype]              # every token alone, from the first
+        assert e(run_schedule(rig, t, [50]), ref) < TOL[dtype]            # a prompt, then decoding
+
+
+@pytest.mark.parametrize("cuts", [[2, 2, 2, 3, 5, 64, 1, 2, 40], [39, 2, 41, 2, 63, 1, 64], [128, 2], [1, 1, 1, 2, 200]])
+def test_portions_of_any_size(cuts):
+    t = toks(230, seed=11)
+    with Rig(FULL, "float32") as rig:
+        assert err(run_schedule(rig, t, cuts), rig.oracle(t)) < TOL["float32"]
+
+
+def test_results_do_not_depend_on_the_cut_beyond_rounding():
+    t = toks(130, seed=13)
+    with Rig(FULL, "bfloat16") as rig:
+        a = run_schedule(rig, t, [130])
+        b = run_schedule(rig, t, [3, 61, 2, 30])
+        assert err16(b, a.cpu()) < 2e-2
+
+
+def test_unequal_requests_in_one_batch_equal_each_alone():
+    lens = [5, 77, 140, 33]
+    seqs = [toks(n, seed=20 + i) for i, n in enumerate(lens)]
+    with Rig(FULL, "float32") as rig:
+        refs = [rig.oracle(s) for s in seqs]
+        at = [0] * 4
+        portions = [[2, 3], [40, 2, 35], [64, 64, 12], [1] * 33]
+        got = [[] for _ in seqs]
+        step = 0
+        while any(at[i] < lens[i] for i in range(4)):
+            entries = []
+            for i in range(4):
+                if at[i] < lens[i] and (step + i) % 3 != 2:              # requests sit out some steps
+                    n = portions[i][0] if portions[i] else 1
+                    portions[i] = portions[i][1:]
+                    part = seqs[i][at[i]:at[i] + n]
+                    entries.append((f"q{i}", part, list(range(len(part)))))
+                    at[i] += len(part)
+            step += 1
+            if not entries:
+                continue
+            lg = rig.eng.step(entries)
+            row = 0
+            for rid, part, _ in entries:
+                got[int(rid[1:])].append(lg[row:row + len(part)])
+                row += len(part)
+        for i in range(4):
+            assert err(torch.cat(got[i]), refs[i]) < TOL["float32"], f"request {i}"
+
+
+def test_pages_and_slots_are_reused():
+    """a pool of 4 pages and 2 slots serves 6 requests two at a time; every pass of the loop has its own pages and
+    state in the slot, and a request that does not fit is refused without disturbing the live ones"""
+    from dnet_b200._cabi import DnError
+
+    with Rig(FULL, "float32", max_tokens=256, max_seqs=2, max_batch_tokens=256) as rig:
+        for rnd in range(3):
+            a, b = toks(100 + rnd, seed=30 + rnd), toks(120 - rnd, seed=40 + rnd)
+            la = rig.eng.step([("a", a[:70], []), ("b", b[:3], [])])
+            assert la is None
+            la = rig.eng.step([("a", a[70:], list(range(len(a) - 70))), ("b", b[3:], list(range(len(b) - 3)))])
+            assert err(la[:len(a) - 70], rig.oracle(a)[70:]) < TOL["float32"]
+            assert err(la[len(a) - 70:], rig.oracle(b)[3:]) < TOL["float32"]
+            assert rig.model.free_pages == 0 and rig.model.free_slots == 0
+            with pytest.raises(DnError):
+                rig.eng.step([("a", toks(60), [])])                        # a fifth page does not exist
+            with pytest.raises(DnError):
+                rig.eng.step([("c", [1], [])])                            # nor a third slot
+            rig.eng.live.pop("c", None)
+            rig.eng.finish("a")
+            rig.eng.finish("b")
+            assert rig.model.free_pages == 4 and rig.model.free_slots == 2
+
+
+def test_a_freed_slot_starts_from_zero_state():
+    """recurrent states and the shifted row of a slot's last user must not leak into the next one"""
+    cfg = config([wkv(), par(MOE)], loop=(0, 2, 2))
+    with Rig(cfg, "float32", max_seqs=1) as rig:
+        first = toks(80, seed=50)
+        rig.eng.step([("x", first, [])])
+        rig.eng.finish("x")
+        t = toks(40, seed=51)
+        assert err(run_schedule(rig, t, [10, 2]), rig.oracle(t)) < TOL["float32"]
+
+
+# -- keys far away and the sink, with scores made to stand out --------------------------------------------------------
+def far_key_setup(sink: float):
+    """One parallel layer whose left half matches an early key from pages away: keys are projected with minus the
+    first query head's weights, so a query scores -|q|^2 against its own token and +|q|^2 against a token whose
+    mixer input points the other way.  The norm before the mixer is made odd (no bias), and token 63's embedding is
+    minus token 62's: token 63 appears once, at position 3, and token 62 ends the prompt."""
+    cfg = config([par(left={"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 16, "scale": 0.25, "softcap": 30.0}, left_scale=1.0, right_scale=0.05)],
+                 vocab=64)
+    w = fo.random_weights(cfg, 70)
+    g = torch.Generator().manual_seed(71)
+    e = w["embed"].clone()
+    e[63] = -e[62]
+    w["embed"] = e
+    for n in ("embed.norm.b", "l0.norm1.b"):
+        w[n] = torch.zeros_like(w[n])
+    w["l0.mix.left.k"] = -w["l0.mix.left.q"][:64].clone()
+    w["l0.mix.left.sink"] = torch.full_like(w["l0.mix.left.sink"], sink)
+    t = torch.randint(0, 62, (700,), generator=g).tolist()
+    t[3] = 63
+    t += [62] * 6
+    return cfg, w, t
+
+
+def test_far_key_among_hundreds():
+    cfg, w, t = far_key_setup(sink=-4.0)
+    with Rig(cfg, "float32", weights=w) as rig:
+        ref = rig.oracle(t)
+        t_without = list(t)
+        t_without[3] = 5
+        assert err(rig.oracle(t_without)[-6:], ref[-6:]) > 100 * TOL["float32"]       # the far key matters
+        assert err(run_schedule(rig, t, [len(t)]), ref) < TOL["float32"]
+        assert err(run_schedule(rig, t, [300, 2, 250, 148]), ref) < TOL["float32"]    # the last six decoded one by one
+    with Rig(cfg, "bfloat16", weights=w) as rig:
+        assert err16(run_schedule(rig, t, [300, 2, 250, 148])[-6:], ref[-6:]) < TOL["bfloat16"]
+
+
+def test_a_sink_that_is_left_out_shows():
+    """a sink as large as the best score takes half of the weight: the oracle without it differs, the product agrees
+    with the oracle that has it, in prompts (both attention kernels) and in decoding"""
+    cfg, w, t = far_key_setup(sink=6.0)
+    t = t[:200] + t[-6:]
+    w_none = dict(w)
+    w_none["l0.mix.left.sink"] = torch.full_like(w["l0.mix.left.sink"], -60.0)
+    ref = fo.forward(cfg, w, t)
+    assert err(fo.forward(cfg, w_none, t), ref) > 100 * TOL["float32"]
+    for dtype in ("float32", "bfloat16"):
+        with Rig(cfg, dtype, weights=w) as rig:
+            e = err16 if dtype == "bfloat16" else err
+            assert e(run_schedule(rig, t, [len(t)]), ref) < TOL[dtype]
+            assert e(run_schedule(rig, t, [150, 2, 40]), ref) < TOL[dtype]
+
+
+def test_score_cap_and_page_borders():
+    """scores far beyond the cap (every visible key then weighs nearly the same): a cap applied before the scale, or
+    left out, shows; prompts end and decoding starts at, just before and just after a page border"""
+    cfg = config([par(left={"scale": 3.0, "softcap": 1.5}, left_scale=1.0, right_scale=0.2), wkv()])
+    w = fo.random_weights(cfg, 75)
+    uncapped = copy.deepcopy(cfg)
+    uncapped["layers"][0]["mixer"]["left"]["softcap"] = 400.0
+    t = toks(140, seed=76)
+    ref = fo.forward(cfg, w, t)
+    assert err(fo.forward(uncapped, w, t), ref) > 100 * TOL["float32"]
+    with Rig(cfg, "float32", weights=w) as rig:
+        for first in (63, 64, 65, 127, 128, 129):
+            assert err(run_schedule(rig, t, [first]), ref) < TOL["float32"], f"prompt of {first}"
+        assert err(run_schedule(rig, t, [62, 2, 62, 2, 2]), ref) < TOL["float32"]
+
+
+def test_state_carried_across_portions_shows_when_lost():
+    """slow decays (tau large, bonus small): the recurrent state holds the whole past, so a state or a shifted row
+    that is lost at a cut changes everything after it"""
+    cfg = config([par(right={"tau": 64.0}, left_scale=0.05, right_scale=2.0), wkv()], loop=(0, 2, 2))
+    w = fo.random_weights(cfg, 77)
+    w["l1.mix.w0"] = torch.full_like(w["l1.mix.w0"], -5.0)
+    t = toks(100, seed=78)
+    ref = fo.forward(cfg, w, t)
+    assert err(fo.forward(cfg, w, t[50:]), ref[50:]) > 100 * TOL["float32"]
+    with Rig(cfg, "float32", weights=w) as rig:
+        assert err(run_schedule(rig, t, [50, 2, 3, 30]), ref) < TOL["float32"]
+
+
+def test_first_tokens_of_a_sequence():
+    with Rig(FULL, "float32") as rig:
+        for n in (1, 2, 3, 4):
+            t = toks(n, seed=80 + n)
+            assert err(run_schedule(rig, t, [n]), rig.oracle(t)) < TOL["float32"]
+            assert err(run_schedule(rig, t, []), rig.oracle(t)) < TOL["float32"]
+
+
+def test_long_decoding():
+    t = toks(300, seed=90)
+    with Rig(FULL, "float32") as rig:
+        assert err(run_schedule(rig, t, [20]), rig.oracle(t)) < TOL["float32"]
+
+
+def test_a_step_larger_than_the_batch_buffer_is_cut_inside():
+    t = toks(300, seed=95)
+    with Rig(FULL, "float32", max_batch_tokens=64) as rig:
+        got = rig.eng.step([("a", t[:290], [0, 63, 64, 289]), ("b", t[:70], [69])])
+        ref = rig.oracle(t)
+        assert err(got[:4], ref[[0, 63, 64, 289]]) < TOL["float32"]
+        assert err(got[4:], ref[[69]]) < TOL["float32"]
+
+
+def test_graph_replay_equals_launch_by_launch_decoding():
+    t = toks(60, seed=97)
+    with Rig(FULL, "bfloat16") as rig:
+        a = run_schedule(rig, t, [20])
+        rig.model.set_graphs(False)
+        b = run_schedule(rig, t, [20])
+        assert torch.equal(a, b)
+
+
+# -- the token loop ---------------------------------------------------------------------------------------------------
+def test_greedy_generation_through_the_batcher():
+    from dnet_b200.shard.batching import GenRequest
+
+    with Rig(FULL, "float32", max_tokens=320, max_seqs=2) as rig:
+        rig.eng.step_tokens = 48
+        reqs = [GenRequest(f"g{i}", toks(n, seed=100 + i), max_new_tokens=m) for i, (n, m) in enumerate([(30, 6), (100, 4), (3, 9), (65, 5)])]
+        out = rig.eng.generate(reqs)
+        assert rig.model.free_slots == 2 and rig.model.free_pages == 5
+        for r in reqs:
+            seq = list(r.prompt)
+            for tok in out[r.id]:
+                lg = rig.oracle(seq)[-1]
+                top2 = torch.topk(lg, 2).values
+                if float(top2[0] - top2[1]) > 1e-3:           # a near tie may fall either way
+                    assert tok == int(lg.argmax()), f"{r.id} at length {len(seq)}"
+                seq.append(tok)
+
+
+def test_command_lines_on_a_checkpoint_folder(tmp_path):
+    """bin/trace_run on a folder with config.json and model.safetensors: the class is picked by the
+    config's architecture, the sizes the config lacks come from the tensors' shapes"""
+    import json
+    import os
+    import struct
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    cfg = config([wkv(MOE), par(MOE)], loop=(1, 2, 2))
+    w = fo.random_weights(cfg, 110, rank=5)
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(cfg))
+    header, blobs, at = {}, [], 0
+    for k, v in w.items():
+        raw = v.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        header[k] = {"dtype": "BF16", "shape": list(v.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    (folder / "model.safetensors").write_bytes(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    t = toks(70, seed=111)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": t[:50], "want": [49]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": t[50:52], "want": [0, 1]}, {"id": "b", "tokens": t[:9], "want": [8]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": t[52:], "want": [17]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ref = fo.forward(cfg, w, t)
+    got = [torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4")).view(-1, cfg["vocab"]) for i in range(3)]
+    assert err(got[0], ref[[49]]) < TOL["float32"]
+    assert err(got[1], torch.cat([ref[[50, 51]], fo.forward(cfg, w, t[:9])[[8]]])) < TOL["float32"]
+    assert err(got[2], ref[[69]]) < TOL["float32"]
