@@ -2,6 +2,7 @@
 own mechanisms against independent formulations, and the batcher's token loop over a fake model."""
 from __future__ import annotations
 
+import pytest
 import torch
 
 from oracle import seqmix_oracle as so
@@ -49,17 +50,99 @@ def test_checkpoint_names_reach_the_registry():
 
 
 def test_header_and_binding_agree():
+    import re
+
     from dnet_b200 import _seqabi
 
     assert set(_seqabi.declared_symbols()) == set(_seqabi._PROTOS)
-    txt = _seqabi.HEADER_PATH.read_text()
-    order = [n.strip() for n in txt.split("enum {", 1)[1].split("DN_SQ_COUNT", 1)[0].replace("= 0", "").replace("\n", " ").split(",") if n.strip()]
+    txt = re.sub(r"/\*.*?\*/", "", _seqabi.HEADER_PATH.read_text(), flags=re.S)
+    body = txt.split("DN_SQ_NORM1 = 0", 1)[1].split("DN_SQ_COUNT", 1)[0]
+    order = ["DN_SQ_NORM1"] + [n.strip() for n in body.replace("\n", " ").split(",") if n.strip()]
     assert len(order) == len(_seqabi.LAYER_SLOT)
-    spell = {"OUT_NORM": "mix.norm", "NORM1": "norm1", "NORM2": "norm2", "GATE": "mlp.gate", "UP": "mlp.up", "DOWN": "mlp.down"}
+    spell = {"OUT_NORM": "mix.norm", "NORM1": "norm1", "NORM2": "norm2", "GATE": "mlp.gate", "UP": "mlp.up", "DOWN": "mlp.down",
+             "HEAD_GATE": "head_gate", "SINK": "sink", "BONUS": "bonus", "DECAY1": "decay1", "DECAY2": "decay2", "DECAY_B": "decay.b",
+             "ROUTER": "router", "ROUTER_B": "router.b", "SH_GATE": "shared.gate", "SH_UP": "shared.up", "SH_DOWN": "shared.down"}
     for i, name in enumerate(order):
         n = name[len("DN_SQ_"):]
-        want = spell.get(n) or (n.lower().replace("_", ".", 1) if n.startswith("HC") else "mix." + {"A_LOG": "A_log", "DT_BIAS": "dt_bias"}.get(n, n.lower().replace("_", ".")))
+        if n in spell:
+            want = spell[n]
+        elif n.startswith(("HC", "NORM", "POST", "R_", "MU_")):
+            want = n.lower().replace("_", ".", 1)
+        else:
+            want = "mix." + {"A_LOG": "A_log", "DT_BIAS": "dt_bias"}.get(n, n.lower().replace("_", "."))
         assert _seqabi.LAYER_SLOT[want] == i, (name, want)
+    model = [n.strip().split("=")[0].strip() for n in txt.split("DN_SQ_COUNT,", 1)[1].split("}", 1)[0].replace("\n", " ").split(",") if n.strip()]
+    assert [_seqabi.MODEL_SLOT[k] for k in ("embed", "final.norm", "head", "final.norm.b", "final.norm.alpha", "embed.norm", "embed.norm.b",
+                                           "embed.norm.alpha", "loop.in")] == list(range(100, 100 + len(model)))
+
+
+def _filinex_cfg():
+    moe = {"kind": "moe", "router": {"experts": 5, "top": 2}, "expert": {"ff": 24, "limit": 1.5}, "shared": {"ff": 16, "limit": 0.5}}
+    return {"architecture": "Filinex", "vocab": 50, "width": 32, "norm": {"eps": 1e-5}, "logit_softcap": 7.0,
+            "loop": {"start": 1, "stop": 3, "times": 4},
+            "layers": [{"type": "wkv", "mixer": {"heads": 2, "dim": 8}, "mlp": moe},
+                       {"type": "parallel", "mixer": {"left": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "scale": 0.2, "softcap": 20.0},
+                                                      "right": {"heads": 3, "dim": 8, "vdim": 4, "tau": 8.0}, "left_scale": 0.7, "right_scale": 0.3},
+                        "mlp": {**moe, "shared": None}},
+                       {"type": "wkv", "mixer": {"heads": 1, "dim": 16}, "mlp": None}]}
+
+
+def test_filinex_config_and_checkpoint_names():
+    """every tensor of a checkpoint finds its place: the names the oracle writes, through the class's aliases, are
+    the names the model expects, with the shapes; sizes the config lacks come from the tensors"""
+    from dnet_b200 import _seqabi
+    from dnet_b200.core.models import ring_model_class
+    from dnet_b200.core.models.seqmix import _LAYER_KEY, parse_layer_list
+    from oracle import filinex_oracle as fo
+
+    cfg = _filinex_cfg()
+    cls = ring_model_class("filinex")
+    shapes = fo.tensor_shapes(cfg, rank=6)
+    shapes["l2.mix.v"] = shapes["l2.mix.g"] = (24, 32)       # a value size that differs from the key size
+    shapes["l2.mix.norm"], shapes["l2.mix.o"] = (24,), (32, 24)
+    sc, layers = parse_layer_list(cfg, cls.family, shapes)
+    assert (sc.norm_kind, sc.post_norm, sc.embed_norm) == (_seqabi.DN_NORM_DYT, 1, 1)
+    assert (sc.loop_start, sc.loop_stop, sc.loop_times) == (1, 3, 4) and abs(sc.logit_softcap - 7.0) < 1e-6
+    assert [l.mixer for l in layers] == [_seqabi.DN_MIX_WKV, _seqabi.DN_MIX_PARALLEL, _seqabi.DN_MIX_WKV]
+    assert (layers[0].rank, layers[1].rank, layers[2].vdim) == (6, 6, 24)
+    assert (layers[1].sink, layers[1].out_gate, layers[1].qk_norm, layers[1].r_heads, layers[1].shared_ff) == (1, 1, 0, 3, 0)
+    assert (layers[0].experts, layers[0].top, layers[0].ff, layers[0].shared_ff, layers[2].ff) == (5, 2, 24, 16, 0)
+    with pytest.raises(ValueError):
+        parse_layer_list(cfg, cls.family, None)              # the inner size of the decay projection is in no config key
+    m = cls.__new__(cls)
+    m.config, m._cfg_struct, m._layer_structs, m.hidden_size, m.vocab_size = cfg, sc, layers, sc.width, sc.vocab
+    want = m.expected_tensors()
+    got = {}
+    for key, sh in shapes.items():
+        if _LAYER_KEY.match(key):
+            lname, suffix = key.split(".", 1)
+            kind = cfg["layers"][int(lname[1:])]["type"]
+            suffix = cls.tensor_alias.get(kind, {}).get(suffix, cls.tensor_alias["*"].get(suffix, suffix))
+            key = f"{lname}.{suffix}"
+        got[key] = tuple(sh)
+    assert got == {k: tuple(v) for k, v in want.items()}
+    for k in want:
+        if _LAYER_KEY.match(k) and ".mlp.e" not in k:
+            assert k.split(".", 1)[1] in _seqabi.LAYER_SLOT, k
+
+
+def test_filinex_oracle_recurrences_by_hand():
+    from oracle import filinex_oracle as fo
+
+    one = torch.ones(2, 1, dtype=torch.float64)
+    v = torch.tensor([[1.0], [10.0]], dtype=torch.float64)
+    half = torch.full((2, 1), 0.5, dtype=torch.float64)
+    # read after the write: o_1 = 0.5 * 1 + 10
+    assert torch.allclose(fo.decayed_outer_recurrence(one, one, v, half, None)[:, 0], torch.tensor([1.0, 10.5], dtype=torch.float64))
+    # read before it, the current token through the bonus: o_0 = 3 * 1, o_1 = 1 + 3 * 10
+    bonus = torch.tensor([3.0], dtype=torch.float64)
+    assert torch.allclose(fo.decayed_outer_recurrence(one, one, v, half, bonus)[:, 0], torch.tensor([3.0, 31.0], dtype=torch.float64))
+    # a sink as large as the only score halves the weight of the only key
+    q = k = torch.ones(1, 1, 1, dtype=torch.float64)
+    val = torch.full((1, 1, 1), 8.0, dtype=torch.float64)
+    assert torch.allclose(fo.sink_attention(q, k, val, 2.0, 0.0, torch.tensor([2.0])), torch.full((1, 1, 1), 4.0, dtype=torch.float64))
+    # the cap bounds the scaled score: with cap 1 a score of 100 counts as 1
+    assert torch.allclose(fo.sink_attention(q, k, val, 100.0, 1.0, torch.tensor([1.0])), torch.full((1, 1, 1), 4.0, dtype=torch.float64), atol=1e-9)
 
 
 def test_oracle_conv_is_a_causal_depthwise_fir():
