@@ -19,14 +19,20 @@
 //                residual or feed fp32 gates)
 //   EPI_GEGLU  : two weight tiles like EPI_SWIGLU; y = T(gelu_tanh(acc_g) * acc_u), the activation and the product
 //                in fp32 with one rounding                     -> Y[t][n]
+//   EPI_CGLU   : two weight tiles; g = min(acc_g, limit), u = clamp(acc_u, -limit, limit), y = T(g sigmoid(1.702 g) (u + 1))
+//
+// GROUPED: one launch over many weight matrices of one shape (routed experts).  The token rows are sorted by matrix
+// into tiles of BN rows that never span two matrices; a device table gives every token tile its matrix, first row
+// and row count, and the weights' TMA descriptors lie in an array in global memory (written by the host before the
+// launch).  The number of token tiles is read from device memory, so the host never learns the routing.
 #pragma once
 #include <cuda.h>
 #include "dn_megakernel.cuh"
 
 namespace dn {
 
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_GEGLU = 4 };
-__host__ __device__ constexpr bool epi_two_weights(int epi) { return epi == EPI_SWIGLU || epi == EPI_GEGLU; }
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_GEGLU = 4, EPI_CGLU = 5 };
+__host__ __device__ constexpr bool epi_two_weights(int epi) { return epi == EPI_SWIGLU || epi == EPI_GEGLU || epi == EPI_CGLU; }
 
 constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
 constexpr int TC_BK = 64;         // k-step: 64 bf16 = 128 bytes = one swizzle span
@@ -40,6 +46,10 @@ struct TcParams {
   int ldr;
   const bf16* bias;               // [N] or null
   unsigned int* err;
+  float limit;                    // EPI_CGLU
+  // GROUPED: token tile tt uses the matrix g_tile_e[tt] on the rows [g_tile_r0[tt], + g_tile_rows[tt]) of X and Y
+  const int32_t *g_tile_e, *g_tile_r0, *g_tile_rows, *g_ntiles;
+  const CUtensorMap *g_mapW, *g_mapW2;      // [matrices], 64-byte aligned, in global memory
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -93,7 +103,7 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int BN, int EPI, int STAGES>
+template <int BN, int EPI, int STAGES, bool GROUPED = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapW2,
           const __grid_constant__ CUtensorMap mapX, const TcParams p) {
@@ -116,7 +126,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (p.N + TC_BM - 1) / TC_BM;
-  const int t_tiles = (p.T + BN - 1) / BN;
+  const int t_tiles = GROUPED ? *p.g_ntiles : (p.T + BN - 1) / BN;
   const int total_tiles = n_tiles * t_tiles;
   const int k_steps = p.K / TC_BK;
 
@@ -140,13 +150,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
       int stage = 0; uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const int tt = tile % t_tiles, nt = tile / t_tiles;     // token tiles of one weight tile run back to back (weights hit L2)
+        if (GROUPED) {      // descriptors read from global memory: make the host's writes visible to the TMA unit
+          asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(p.g_mapW + p.g_tile_e[tt]) : "memory");
+          if (NA == 2) asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(p.g_mapW2 + p.g_tile_e[tt]) : "memory");
+        }
         for (int ks = 0; ks < k_steps; ++ks) {
           mbar_wait(&empty[stage], phase ^ 1u, p.err);
           mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
           unsigned char* sa = smem + (size_t)stage * STAGE_BYTES;
-          tma_load_2d(sa, &mapW, ks * TC_BK, nt * TC_BM, &full[stage]);
-          if (NA == 2) tma_load_2d(sa + A_BYTES, &mapW2, ks * TC_BK, nt * TC_BM, &full[stage]);
-          tma_load_2d(sa + NA * A_BYTES, &mapX, ks * TC_BK, tt * BN, &full[stage]);
+          tma_load_2d(sa, GROUPED ? p.g_mapW + p.g_tile_e[tt] : &mapW, ks * TC_BK, nt * TC_BM, &full[stage]);
+          if (NA == 2) tma_load_2d(sa + A_BYTES, GROUPED ? p.g_mapW2 + p.g_tile_e[tt] : &mapW2, ks * TC_BK, nt * TC_BM, &full[stage]);
+          tma_load_2d(sa + NA * A_BYTES, &mapX, ks * TC_BK, GROUPED ? p.g_tile_r0[tt] : tt * BN, &full[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -195,6 +209,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
       const uint32_t trow = tmem_base + ab * ACC_COLS + ((uint32_t)(ew * 32) << 16);
       float bias = 0.f;
       if (EPI == EPI_STORE && p.bias != nullptr && n < p.N) bias = __bfloat162float(p.bias[n]);
+      const int t_base = GROUPED ? p.g_tile_r0[tt] : tt * BN;
+      const int t_end = GROUPED ? t_base + p.g_tile_rows[tt] : p.T;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         float v[16], v2[16];
@@ -203,8 +219,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
         if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int t = tt * BN + c + j;
-            if (t < p.T) {
+            const int t = t_base + c + j;
+            if (t < t_end) {
               if (EPI == EPI_STORE_F32) {
                 reinterpret_cast<float*>(p.Y)[(size_t)t * p.ldy + p.col0 + n] = v[j];
                 continue;
@@ -213,6 +229,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
               if (EPI == EPI_GEGLU) {
                 const float g = v[j];
                 y = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * v2[j];
+              } else if (EPI == EPI_CGLU) {
+                const float g = fminf(v[j], p.limit), u = fminf(fmaxf(v2[j], -p.limit), p.limit);
+                y = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
               } else if (EPI == EPI_STORE) {
                 y = v[j] + bias;
               } else if (EPI == EPI_RESID) {

@@ -64,6 +64,10 @@ struct SeqLayer {
   float* inv_freq;              // [rot/2] device
   std::vector<const void*> etab_h;   // routed experts: [3][E] gate, up, down
   const void** etab_d;
+  CUtensorMap* emaps_d;              // [3][E] TMA descriptors of the experts' matrices, in device memory (bf16 mode)
+  std::vector<char> emap_ok;
+  CUtensorMap x_eact;                // the experts' activations [pairs, ff], 64-row boxes
+  bool x_eact_ok;
 };
 // One run of a layer.  A layer inside the loop runs loop_times times on the same weights; every run has its own
 // pages, carried inputs and recurrent state.
@@ -80,8 +84,9 @@ struct dn_seq_model {
   std::vector<Run> runs;
   const void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
   const void* mw[16] = {nullptr};     // the other model tensors, by (which - DN_SQ_EMBED)
-  CUtensorMap tm_loop_in;
-  bool tm_loop_ok = false;
+  CUtensorMap tm_loop_in, x_xg;       // x_xg: the tokens' rows sorted by expert [pairs, W], 64-row boxes
+  bool tm_loop_ok = false, x_xg_ok = false;
+  void* xg = nullptr;
   XMaps x_cat, x_xm[SHIFT_MAX];
   size_t esz = 2;
   int S1 = 1, MB = 0, max_pages = 0;
@@ -188,7 +193,7 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   cudaDeviceSynchronize();
   void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
                   m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err, m->y2, m->x0, m->dz, m->rwt,
-                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles};
+                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles, m->xg};
   for (void* p : ptrs) if (p) cudaFree(p);
   for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
   if (m->lg_buf) cudaFree(m->lg_buf);
@@ -196,7 +201,7 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   for (cudaEvent_t ev : m->prof_pool) cudaEventDestroy(ev);
   for (void* p : m->kpool) if (p) cudaFree(p);
   for (void* p : m->vpool) if (p) cudaFree(p);
-  for (auto& l : m->L) { if (l.inv_freq) cudaFree(l.inv_freq); if (l.etab_d) cudaFree((void*)l.etab_d); }
+  for (auto& l : m->L) { if (l.inv_freq) cudaFree(l.inv_freq); if (l.etab_d) cudaFree((void*)l.etab_d); if (l.emaps_d) cudaFree(l.emaps_d); }
   if (m->stage_h) cudaFreeHost(m->stage_h);
   if (m->bt_h) cudaFreeHost(m->bt_h);
   if (m->staged) cudaEventDestroy(m->staged);
@@ -235,6 +240,8 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
     memset(l.tm_ok, 0, sizeof(l.tm_ok));
     l.inv_freq = nullptr;
     l.etab_d = nullptr;
+    l.emaps_d = nullptr;
+    l.x_eact_ok = false;
     l.Rc = l.Rv = 0;
     const dn_seq_layer_cfg& c = l.c;
     if (c.heads <= 0 || c.kv_heads <= 0 || c.heads % c.kv_heads || c.dim <= 0 || c.vdim <= 0) {
@@ -299,6 +306,8 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
       }
       l.etab_h.assign((size_t)3 * c.experts, nullptr);
       if ((rc = dalloc(&l.etab_d, (size_t)3 * c.experts * sizeof(void*))) != DN_OK) break;
+      l.emap_ok.assign((size_t)3 * c.experts, 0);
+      if (cfg->dtype == DN_SEQ_BF16 && (rc = dalloc(&l.emaps_d, (size_t)3 * c.experts * sizeof(CUtensorMap))) != DN_OK) break;
       mpairs = std::max(mpairs, c.top);
       meff = std::max(meff, c.ff);
       mexp = std::max(mexp, c.experts);
@@ -364,6 +373,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
     m->max_tiles = (int)(P / MOE_ROWS) + mexp + 1;
     DA(m->ridx, P * 4); DA(m->rpos, P * 4); DA(m->rtok, P * 4); DA(m->rwt, P * 4); DA(m->tiles, ((size_t)3 * m->max_tiles + 4) * 4);
     DA(m->eact, P * meff * e); DA(m->eo, P * W * 4);
+    if (cfg->dtype == DN_SEQ_BF16) DA(m->xg, P * W * e);
   }
   DA(m->h, MB * W * e); DA(m->uq, MB * mq * e); DA(m->uk, MB * mk * e); DA(m->uv, MB * mv * e); DA(m->qb, MB * mq * e);
   DA(m->mo, MB * mo * e); DA(m->gt, MB * mo * e); DA(m->act, MB * mff * e);
@@ -381,6 +391,11 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
       if (l.c.rank > 0) make_xmaps(&l.x_lr, m->lr, m->MB, l.c.rank);
       const int fa = l.c.mlp_kind == DN_MLP_MOE ? l.c.shared_ff : l.c.ff;
       if (fa > 0) make_xmaps(&l.x_act, m->act, m->MB, fa);
+    }
+    if (m->xg) {
+      m->x_xg_ok = make_tmap(&m->x_xg, m->xg, m->MB * mpairs, cfg->width, MOE_ROWS);
+      for (auto& l : m->L)
+        if (l.c.mlp_kind == DN_MLP_MOE && l.c.ff > 0) l.x_eact_ok = make_tmap(&l.x_eact, m->eact, m->MB * l.c.top, l.c.ff, MOE_ROWS);
     }
     if (m->cat) make_xmaps(&m->x_cat, m->cat, m->MB, 2 * cfg->width);
     if (m->xm) for (int i = 0; i < SHIFT_MAX; i++) make_xmaps(&m->x_xm[i], (char*)m->xm + (size_t)i * MB * W * e, m->MB, cfg->width);
@@ -454,6 +469,12 @@ extern "C" int dn_seq_bind_expert(dn_seq_model* m, int layer, int expert, int wh
   const size_t at = (size_t)which * l.c.experts + expert;
   l.etab_h[at] = p;
   CK(cudaMemcpy((void*)(l.etab_d + at), &p, sizeof(void*), cudaMemcpyHostToDevice));
+  if (l.emaps_d) {
+    CUtensorMap tm;
+    const bool down = which == DN_SQ_E_DOWN;
+    l.emap_ok[at] = make_tmap(&tm, p, down ? m->cfg.width : l.c.ff, down ? l.c.ff : m->cfg.width, dn::TC_BM) ? 1 : 0;
+    if (l.emap_ok[at]) CK(cudaMemcpy(l.emaps_d + at, &tm, sizeof(tm), cudaMemcpyHostToDevice));
+  }
   return DN_OK;
 }
 extern "C" int dn_seq_layer_runs(dn_seq_model* m) { return m ? (int)m->runs.size() : DN_EINVAL; }
@@ -552,10 +573,11 @@ struct LinMaps { const CUtensorMap* w; const CUtensorMap* w2; const XMaps* x; };
 template <class T>
 static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32,
                           int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}, float alim = 0.f) {
-  if (std::is_same<T, bf16>::value && N >= 16 && O >= 32 && tm.w && tm.x && tm.x->ok && (act == ACT_NONE || (act == ACT_GEGLU && tm.w2))) {
+  if (std::is_same<T, bf16>::value && N >= 16 && O >= 32 && tm.w && tm.x && tm.x->ok && (act == ACT_NONE || ((act == ACT_GEGLU || act == ACT_CGLU) && tm.w2))) {
     dn::TcParams p;
     memset(&p, 0, sizeof(p));
-    p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err;
+    p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err; p.limit = alim;
+    if (act == ACT_CGLU) return gemm_tc<dn::EPI_CGLU>(*tm.w, *tm.w2, *tm.x, p, s);
     if (act) return gemm_tc<dn::EPI_GEGLU>(*tm.w, *tm.w2, *tm.x, p, s);
     if (out32) return gemm_tc<dn::EPI_STORE_F32>(*tm.w, *tm.w, *tm.x, p, s);
     return gemm_tc<dn::EPI_STORE>(*tm.w, *tm.w, *tm.x, p, s);
@@ -610,6 +632,23 @@ static cudaError_t mark(dn_seq_model* m, int phase, cudaStream_t s) {
   return cudaEventRecord(ev, s);
 }
 
+// one launch of the tcgen05 GEMM over all experts of a layer (token tiles of MOE_ROWS rows from the plan)
+template <int EPI>
+static cudaError_t gemm_tc_grouped(const CUtensorMap& x, const dn::TcParams& p, cudaStream_t s) {
+  constexpr int NA = dn::epi_two_weights(EPI) ? 2 : 1;
+  constexpr int STAGES = NA == 2 ? 5 : 8;
+  constexpr size_t smem = (size_t)STAGES * (NA * dn::TC_BM * dn::TC_BK * 2 + MOE_ROWS * dn::TC_BK * 2) + 1024 + 256;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(dn::k_gemm_tc<MOE_ROWS, EPI, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  g_launches++;
+  dn::k_gemm_tc<MOE_ROWS, EPI, STAGES, true><<<g_sms, dn::TC_THREADS, smem, s>>>(x, x, x, p);
+  return cudaGetLastError();
+}
+
 // the expert products of a routed feed-forward: h [N, W] -> m->y [N, W] (routed sum), m->y2 (shared expert, if any)
 template <class T>
 static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
@@ -630,10 +669,26 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
     MoePlan pl{m->rpos, m->rtok, m->tiles, m->tiles + m->max_tiles, m->tiles + 2 * m->max_tiles, m->tiles + 3 * m->max_tiles};
     const int mt = std::min(m->max_tiles, P / MOE_ROWS + E + 1);
     CK(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)(2 * E + 1) * 4, s, (const int32_t*)m->ridx, P, top, E, pl));
-    CK(mark(m, DN_SEQ_PH_MOE_UP, s));
-    CK(launch(k_moe_tiles<T, true>, dim3((lc.ff + 63) / 64, mt), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, pl, m->eact, lc.ff, W, lc.limit));
-    CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
-    CK(launch(k_moe_tiles<T, false>, dim3((W + 63) / 64, mt), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, pl, m->eo, W, lc.ff, 0.f));
+    bool tc = std::is_same<T, bf16>::value && m->x_xg_ok && l.x_eact_ok && l.emaps_d && lc.ff >= 32 && W >= 32;
+    for (char ok : l.emap_ok) tc = tc && ok;
+    if (tc) {     // bf16 with TMA-able shapes: every expert's tiles in one launch of the tcgen05 GEMM
+      CK(launch(k_moe_gather<T>, dim3(P), dim3(128), 0, s, (const T*)m->h, (const int32_t*)m->rtok, W, (T*)m->xg));
+      dn::TcParams p;
+      memset(&p, 0, sizeof(p));
+      p.err = m->tc_err; p.limit = lc.limit;
+      p.g_tile_e = pl.tile_e; p.g_tile_r0 = pl.tile_r0; p.g_tile_rows = pl.tile_rows; p.g_ntiles = pl.n_tiles;
+      CK(mark(m, DN_SEQ_PH_MOE_UP, s));
+      p.T = P; p.N = lc.ff; p.K = W; p.ldy = lc.ff; p.Y = (dn::bf16*)m->eact; p.g_mapW = l.emaps_d; p.g_mapW2 = l.emaps_d + E;
+      CK(gemm_tc_grouped<dn::EPI_CGLU>(m->x_xg, p, s));
+      CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
+      p.N = W; p.K = lc.ff; p.ldy = W; p.Y = (dn::bf16*)m->eo; p.g_mapW = l.emaps_d + 2 * E; p.g_mapW2 = l.emaps_d + 2 * E;
+      CK(gemm_tc_grouped<dn::EPI_STORE_F32>(l.x_eact, p, s));
+    } else {
+      CK(mark(m, DN_SEQ_PH_MOE_UP, s));
+      CK(launch(k_moe_tiles<T, true>, dim3((lc.ff + 63) / 64, mt), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, pl, m->eact, lc.ff, W, lc.limit));
+      CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
+      CK(launch(k_moe_tiles<T, false>, dim3((W + 63) / 64, mt), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, pl, m->eo, W, lc.ff, 0.f));
+    }
   }
   CK(launch(k_moe_combine, dim3((unsigned)(((size_t)N * W + 255) / 256)), dim3(256), 0, s, (const float*)m->eo, (const float*)m->rwt, (const int32_t*)m->rpos, N, W, top, m->y));
   if (lc.shared_ff > 0) {

@@ -169,6 +169,19 @@ __global__ void __launch_bounds__(256) k_moe_rows(const T* __restrict__ X, const
     linear_row<T>(X + (size_t)p * K, (const T*)etab[2 * E + e], (const T*)nullptr, (float*)Y + (size_t)p * O, true, 1, O, K, ACT_NONE, o, 0.f);
 }
 
+// the tokens' rows in the order of the plan (the tensor-core tiles read them with one TMA descriptor): xg[row] = h[row_tok[row]]
+template <class T>
+__global__ void k_moe_gather(const T* __restrict__ h, const int32_t* __restrict__ row_tok, int W, T* __restrict__ xg) {
+  const int row = blockIdx.x;
+  const T* src = h + (size_t)row_tok[row] * W;
+  T* dst = xg + (size_t)row * W;
+  if ((W * (int)sizeof(T)) % 16 == 0) {
+    for (int c = threadIdx.x; c < W * (int)sizeof(T) / 16; c += blockDim.x) reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+  } else {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = src[c];
+  }
+}
+
 // y[n] = sum_j wt[n, j] out[pos[n, j]], the pairs of a token in the order of its choices
 __global__ void k_moe_combine(const float* __restrict__ eo, const float* __restrict__ wt, const int32_t* __restrict__ pos, int N, int W, int top,
                               float* __restrict__ y) {
