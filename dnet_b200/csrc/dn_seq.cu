@@ -66,7 +66,7 @@ struct SeqLayer {
   const void** etab_d;
   CUtensorMap* emaps_d;              // [3][E] TMA descriptors of the experts' matrices, in device memory (bf16 mode)
   std::vector<char> emap_ok;
-  CUtensorMap x_eact;                // the experts' activations [pairs, ff], 64-row boxes
+  CUtensorMap x_eact[2];             // the experts' activations [pairs, ff], 64- and 128-row boxes
   bool x_eact_ok;
 };
 // One run of a layer.  A layer inside the loop runs loop_times times on the same weights; every run has its own
@@ -84,7 +84,7 @@ struct dn_seq_model {
   std::vector<Run> runs;
   const void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
   const void* mw[16] = {nullptr};     // the other model tensors, by (which - DN_SQ_EMBED)
-  CUtensorMap tm_loop_in, x_xg;       // x_xg: the tokens' rows sorted by expert [pairs, W], 64-row boxes
+  CUtensorMap tm_loop_in, x_xg[2];    // x_xg: the tokens' rows sorted by expert [pairs, W], 64- and 128-row boxes
   bool tm_loop_ok = false, x_xg_ok = false;
   void* xg = nullptr;
   XMaps x_cat, x_xm[SHIFT_MAX];
@@ -393,9 +393,10 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
       if (fa > 0) make_xmaps(&l.x_act, m->act, m->MB, fa);
     }
     if (m->xg) {
-      m->x_xg_ok = make_tmap(&m->x_xg, m->xg, m->MB * mpairs, cfg->width, MOE_ROWS);
+      m->x_xg_ok = make_tmap(&m->x_xg[0], m->xg, m->MB * mpairs, cfg->width, 64) && make_tmap(&m->x_xg[1], m->xg, m->MB * mpairs, cfg->width, 128);
       for (auto& l : m->L)
-        if (l.c.mlp_kind == DN_MLP_MOE && l.c.ff > 0) l.x_eact_ok = make_tmap(&l.x_eact, m->eact, m->MB * l.c.top, l.c.ff, MOE_ROWS);
+        if (l.c.mlp_kind == DN_MLP_MOE && l.c.ff > 0)
+          l.x_eact_ok = make_tmap(&l.x_eact[0], m->eact, m->MB * l.c.top, l.c.ff, 64) && make_tmap(&l.x_eact[1], m->eact, m->MB * l.c.top, l.c.ff, 128);
     }
     if (m->cat) make_xmaps(&m->x_cat, m->cat, m->MB, 2 * cfg->width);
     if (m->xm) for (int i = 0; i < SHIFT_MAX; i++) make_xmaps(&m->x_xm[i], (char*)m->xm + (size_t)i * MB * W * e, m->MB, cfg->width);
@@ -633,19 +634,19 @@ static cudaError_t mark(dn_seq_model* m, int phase, cudaStream_t s) {
 }
 
 // one launch of the tcgen05 GEMM over all experts of a layer (token tiles of MOE_ROWS rows from the plan)
-template <int EPI>
+template <int EPI, int BN>
 static cudaError_t gemm_tc_grouped(const CUtensorMap& x, const dn::TcParams& p, cudaStream_t s) {
   constexpr int NA = dn::epi_two_weights(EPI) ? 2 : 1;
-  constexpr int STAGES = NA == 2 ? 5 : 8;
-  constexpr size_t smem = (size_t)STAGES * (NA * dn::TC_BM * dn::TC_BK * 2 + MOE_ROWS * dn::TC_BK * 2) + 1024 + 256;
+  constexpr int STAGES = BN == 128 ? (NA == 2 ? 4 : 6) : (NA == 2 ? 5 : 8);
+  constexpr size_t smem = (size_t)STAGES * (NA * dn::TC_BM * dn::TC_BK * 2 + BN * dn::TC_BK * 2) + 1024 + 256;
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(dn::k_gemm_tc<MOE_ROWS, EPI, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(dn::k_gemm_tc<BN, EPI, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     attr = true;
   }
   g_launches++;
-  dn::k_gemm_tc<MOE_ROWS, EPI, STAGES, true><<<g_sms, dn::TC_THREADS, smem, s>>>(x, x, x, p);
+  dn::k_gemm_tc<BN, EPI, STAGES, true><<<g_sms, dn::TC_THREADS, smem, s>>>(x, x, x, p);
   return cudaGetLastError();
 }
 
@@ -668,9 +669,12 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
   } else {
     MoePlan pl{m->rpos, m->rtok, m->tiles, m->tiles + m->max_tiles, m->tiles + 2 * m->max_tiles, m->tiles + 3 * m->max_tiles};
     const int mt = std::min(m->max_tiles, P / MOE_ROWS + E + 1);
-    CK(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)(2 * E + 1) * 4, s, (const int32_t*)m->ridx, P, top, E, pl));
     bool tc = std::is_same<T, bf16>::value && m->x_xg_ok && l.x_eact_ok && l.emaps_d && lc.ff >= 32 && W >= 32;
     for (char ok : l.emap_ok) tc = tc && ok;
+    // rows of a token tile: 128 (the tensor cores read the weight tile once for twice the tokens) when an expert gets
+    // two such tiles on average, else 64 (less padding); the CUDA-core tiles are 64 rows
+    const int tile_rows = tc && P / E >= 256 ? 128 : MOE_ROWS;
+    CK(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)(2 * E + 1) * 4, s, (const int32_t*)m->ridx, P, top, E, tile_rows, pl));
     if (tc) {     // bf16 with TMA-able shapes: every expert's tiles in one launch of the tcgen05 GEMM
       CK(launch(k_moe_gather<T>, dim3(P), dim3(128), 0, s, (const T*)m->h, (const int32_t*)m->rtok, W, (T*)m->xg));
       dn::TcParams p;
@@ -679,10 +683,12 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
       p.g_tile_e = pl.tile_e; p.g_tile_r0 = pl.tile_r0; p.g_tile_rows = pl.tile_rows; p.g_ntiles = pl.n_tiles;
       CK(mark(m, DN_SEQ_PH_MOE_UP, s));
       p.T = P; p.N = lc.ff; p.K = W; p.ldy = lc.ff; p.Y = (dn::bf16*)m->eact; p.g_mapW = l.emaps_d; p.g_mapW2 = l.emaps_d + E;
-      CK(gemm_tc_grouped<dn::EPI_CGLU>(m->x_xg, p, s));
+      if (tile_rows == 128) CK(gemm_tc_grouped<dn::EPI_CGLU, 128>(m->x_xg[1], p, s));
+      else CK(gemm_tc_grouped<dn::EPI_CGLU, 64>(m->x_xg[0], p, s));
       CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
       p.N = W; p.K = lc.ff; p.ldy = W; p.Y = (dn::bf16*)m->eo; p.g_mapW = l.emaps_d + 2 * E; p.g_mapW2 = l.emaps_d + 2 * E;
-      CK(gemm_tc_grouped<dn::EPI_STORE_F32>(l.x_eact, p, s));
+      if (tile_rows == 128) CK(gemm_tc_grouped<dn::EPI_STORE_F32, 128>(l.x_eact[1], p, s));
+      else CK(gemm_tc_grouped<dn::EPI_STORE_F32, 64>(l.x_eact[0], p, s));
     } else {
       CK(mark(m, DN_SEQ_PH_MOE_UP, s));
       CK(launch(k_moe_tiles<T, true>, dim3((lc.ff + 63) / 64, mt), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, pl, m->eact, lc.ff, W, lc.limit));
@@ -712,11 +718,15 @@ static int decay_rule(dn_seq_model* m, const Batch& b, int mode, int H, int dk, 
   int R, P;
   recur_shape(dk, &R, &P);
   dim3 grid(b.E * H, (dv + 31) / 32);
-  const int per = 3 * P * (R + 4) + 32, TB = std::max(1, std::min(16, 4500 / per));
+  const int per = 3 * P * (R + 4) + 32;
+  int TB = std::max(1, std::min(16, 4500 / per));
+  if (TB >= 4) TB &= ~3;      // whole groups of the kernel's four-token batches
   const size_t dsm = (size_t)2 * TB * per * 4;
-#define DR(Rv, Pv) if (R == Rv && P == Pv) CK(launch(k_decay_rule<Rv, Pv>, grid, dim3(32 * Pv), dsm, s, mode, b, H, dk, dv, TB, (const float*)m->qn, \
+#define DR(Rv, Pv, Cp) if (R == Rv && P == Pv) CK(launch(k_decay_rule<Rv, Pv, Cp>, grid, dim3((32 / Cp) * Pv), dsm, s, mode, b, H, dk, dv, TB, (const float*)m->qn, \
                          (const float*)m->kn, (const float*)m->vv, (const float*)m->dz, bonus, m->esz == 4 ? 1 : 0, st, m->delta_stride, m->od))
-  DR(8, 1); DR(8, 2); DR(8, 4); DR(8, 8); DR(16, 8); DR(16, 16); DR(16, 32); DR(32, 32);
+  // one column a thread: 2 and 4 columns (fewer shared-memory reads, fewer warps) measured slower, the token chain has
+  // too few warps left to hide its latency
+  DR(8, 1, 1); DR(8, 2, 1); DR(8, 4, 1); DR(8, 8, 1); DR(16, 8, 1); DR(16, 16, 1); DR(16, 32, 1); DR(32, 32, 1);
 #undef DR
   return DN_OK;
 }

@@ -553,7 +553,7 @@ struct AttnExtra {
   const void* sink;
   const float* gate;
 };
-constexpr int AT_WARPS = 8;
+constexpr int AT_WARPS = 16;
 template <class T>
 __device__ __forceinline__ void ld_vals(float (&v)[8], const T* p, int cnt, bool vec) {
   if (vec) {
@@ -624,6 +624,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[i] *= corr;
     const int cnt = min(32, p - j0 + 1);
+#pragma unroll 4
     for (int t = 0; t < cnt; t++) {
       const float pt = __shfl_sync(0xffffffffu, pj, t);
       const int jj = j0 + t;

@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(128) k_router(const T* __restrict__ h, const T
   }
 }
 
-// pairs sorted by expert: pos[p] = row of pair p, row_tok[row] = its token, and the table of 64-row tiles
+// pairs sorted by expert: pos[p] = row of pair p, row_tok[row] = its token, and the table of tiles of `rows` rows
 struct MoePlan {
   int32_t* pos;        // [P]
   int32_t* row_tok;    // [P]
@@ -61,7 +61,7 @@ struct MoePlan {
   int32_t* n_tiles;    // [1]
 };
 constexpr int MOE_ROWS = 64;
-__global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ idx, int P, int top, int E, MoePlan pl) {
+__global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ idx, int P, int top, int E, int rows, MoePlan pl) {
   extern __shared__ int32_t cnt[];      // [E] counts, [E + 1] offsets
   int32_t* off = cnt + E;
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -72,10 +72,10 @@ __global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ i
     int a = 0, t = 0;
     for (int e = 0; e < E; e++) {
       off[e] = a;
-      for (int r = 0; r < cnt[e]; r += MOE_ROWS, t++) {
+      for (int r = 0; r < cnt[e]; r += rows, t++) {
         pl.tile_e[t] = e;
         pl.tile_r0[t] = a + r;
-        pl.tile_rows[t] = min(MOE_ROWS, cnt[e] - r);
+        pl.tile_rows[t] = min(rows, cnt[e] - r);
       }
       a += cnt[e];
     }

@@ -58,37 +58,42 @@ __global__ void k_decay_prep(int mode, int N, int C, int Cv, const T* __restrict
 }
 
 // The recurrence, token by token.  Columns of M are independent: a block owns 32 columns of one (entry, head); P
-// adjacent lanes share a column, each holding R consecutive rows (P R >= dk) in registers.  State
+// adjacent lanes share a group of CPT columns, each lane holding R consecutive rows (P R >= dk) of those columns in
+// registers (R x CPT state values a thread), so a token's k, q and decay are read once for CPT columns.  State
 // [slot][head][dk][dv] fp32, read once and written once per step.  A token's k, q, decay and the block's 32 values
 // come through shared memory in tiles of TB tokens, copied asynchronously one tile ahead; k, q and the decay lie
-// there as P runs of R values, each run padded by 4 floats (the 16-byte reads of a column's P lanes fall into
-// different banks); rows from dk up are zero.  The read-out sums four interleaved partials over a thread's rows,
-// then the lanes of a column pairwise: an order fixed by (dk, P), whatever the tile size or the cut of a prompt.
-template <int R, int P>
-__global__ void __launch_bounds__(32 * P) k_decay_rule(int mode, Batch b, int H, int dk, int dv, int TB, const float* __restrict__ qn,
-                                                       const float* __restrict__ kn, const float* __restrict__ vv,
-                                                       const float* __restrict__ decay, const void* __restrict__ bonus, int bonus_f32,
-                                                       float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+// there as P runs of R values, each run padded by 4 floats (the 16-byte reads of a group's P lanes fall into
+// different banks); rows from dk up are zero.  The read-out sums a thread's rows in ascending order, then the lanes
+// of a group pairwise: an order fixed by (dk, P), whatever the tile size or the cut of a prompt.  U tokens are
+// taken at a time: their state updates run back to back and their read-outs are reduced together (U x CPT
+// independent shuffle chains in flight).
+template <int R, int P, int CPT>
+__global__ void __launch_bounds__((32 / CPT) * P) k_decay_rule(int mode, Batch b, int H, int dk, int dv, int TB, const float* __restrict__ qn,
+                                                               const float* __restrict__ kn, const float* __restrict__ vv,
+                                                               const float* __restrict__ decay, const void* __restrict__ bonus, int bonus_f32,
+                                                               float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+  static_assert((32 / CPT) * P >= 32 && 32 % CPT == 0, "whole warps");
   extern __shared__ __align__(16) float dsm[];      // 2 x TB x per
   constexpr int KP = P * (R + 4);
   constexpr int per = 3 * KP + 32;                  // k q decay v[32]
+  constexpr int U = CPT >= 4 ? 2 : 4;
   const int e = blockIdx.x / H, h = blockIdx.x % H;
-  const int part = threadIdx.x % P, colb = threadIdx.x / P, col = blockIdx.y * 32 + colb;
+  const int part = threadIdx.x % P, colg = threadIdx.x / P, col0 = blockIdx.y * 32 + colg * CPT;
   const int s0 = b.ent_start[e], s1 = b.ent_start[e + 1];
-  const bool live = col < dv;
   float* Sg = state + (size_t)b.ent_slot[e] * slot_stride + (size_t)h * dk * dv;
   const int r0 = part * R;
-  float S[R], u[R];
+  float S[R][CPT], u[R];
 #pragma unroll
   for (int r = 0; r < R; r++) {
-    S[r] = (live && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col] : 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; c++) S[r][c] = (col0 + c < dv && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col0 + c] : 0.f;
     u[r] = 0.f;
     if (mode == RECUR_BONUS && r0 + r < dk)
       u[r] = bonus_f32 ? ((const float*)bonus)[(size_t)h * dk + r0 + r] : __bfloat162float(((const bf16*)bonus)[(size_t)h * dk + r0 + r]);
   }
   const int C = H * dk, Cv = H * dv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int nwarp = P;
+  constexpr int nwarp = (32 / CPT) * P / 32;
   auto stage = [&](int buf, int n0) {
     const int cnt = min(TB, s1 - n0);
     for (int t = warp; t < cnt; t += nwarp) {
@@ -113,39 +118,66 @@ __global__ void __launch_bounds__(32 * P) k_decay_rule(int mode, Batch b, int H,
     else cp_async_wait<0>();
     __syncthreads();
     const int cnt = min(TB, s1 - n0);
-    for (int t = 0; t < cnt; t++) {
-      const float* in = dsm + ((size_t)buf * TB + t) * per;
-      const float4* k4 = reinterpret_cast<const float4*>(in + part * (R + 4));
-      const float4* q4 = reinterpret_cast<const float4*>(in + KP + part * (R + 4));
-      const float4* d4 = reinterpret_cast<const float4*>(in + 2 * KP + part * (R + 4));
-      const float v = in[3 * KP + colb];
-      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int t0 = 0; t0 < cnt; t0 += U) {
+      float od[U][CPT];
 #pragma unroll
-      for (int j = 0; j < R / 4; j++) {
-        const float4 kv = k4[j], qv = q4[j], dv4 = d4[j];
-        const float kk[4] = {kv.x, kv.y, kv.z, kv.w}, qq[4] = {qv.x, qv.y, qv.z, qv.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
+      for (int uu = 0; uu < U; uu++) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const float kvp = kk[i] * v;
-          if (mode == RECUR_BONUS) {
-            o4[i] = fmaf(fmaf(u[4 * j + i], kvp, S[4 * j + i]), qq[i], o4[i]);
-            S[4 * j + i] = fmaf(dd[i], S[4 * j + i], kvp);
-          } else {
-            S[4 * j + i] = fmaf(dd[i], S[4 * j + i], kvp);
-            o4[i] = fmaf(S[4 * j + i], qq[i], o4[i]);
+        for (int c = 0; c < CPT; c++) od[uu][c] = 0.f;
+        if (t0 + uu < cnt) {
+          const float* in = dsm + ((size_t)buf * TB + t0 + uu) * per;
+          const float4* k4 = reinterpret_cast<const float4*>(in + part * (R + 4));
+          const float4* q4 = reinterpret_cast<const float4*>(in + KP + part * (R + 4));
+          const float4* d4 = reinterpret_cast<const float4*>(in + 2 * KP + part * (R + 4));
+          float v[CPT];
+#pragma unroll
+          for (int c = 0; c < CPT; c++) v[c] = in[3 * KP + colg * CPT + c];
+#pragma unroll
+          for (int j = 0; j < R / 4; j++) {
+            const float4 kv = k4[j], qv = q4[j], dv4 = d4[j];
+            const float kk[4] = {kv.x, kv.y, kv.z, kv.w}, qq[4] = {qv.x, qv.y, qv.z, qv.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+#pragma unroll
+              for (int c = 0; c < CPT; c++) {
+                const float kvp = kk[i] * v[c];
+                float& Sr = S[4 * j + i][c];
+                if (mode == RECUR_BONUS) {
+                  od[uu][c] = fmaf(fmaf(u[4 * j + i], kvp, Sr), qq[i], od[uu][c]);
+                  Sr = fmaf(dd[i], Sr, kvp);
+                } else {
+                  Sr = fmaf(dd[i], Sr, kvp);
+                  od[uu][c] = fmaf(Sr, qq[i], od[uu][c]);
+                }
+              }
+            }
           }
         }
       }
-      float od = (o4[0] + o4[1]) + (o4[2] + o4[3]);
 #pragma unroll
-      for (int x = 1; x < P; x <<= 1) od += __shfl_xor_sync(0xffffffffu, od, x);
-      if (live && part == 0) o[(size_t)(n0 + t) * Cv + h * dv + col] = od;
+      for (int x = 1; x < P; x <<= 1) {
+#pragma unroll
+        for (int uu = 0; uu < U; uu++)
+#pragma unroll
+          for (int c = 0; c < CPT; c++) od[uu][c] += __shfl_xor_sync(0xffffffffu, od[uu][c], x);
+      }
+      if (part == 0) {
+#pragma unroll
+        for (int uu = 0; uu < U; uu++)
+          if (t0 + uu < cnt) {
+#pragma unroll
+            for (int c = 0; c < CPT; c++)
+              if (col0 + c < dv) o[(size_t)(n0 + t0 + uu) * Cv + h * dv + col0 + c] = od[uu][c];
+          }
+      }
     }
     __syncthreads();      // the tile is read out before the copy after next lands in it
   }
 #pragma unroll
   for (int r = 0; r < R; r++)
-    if (live && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col] = S[r];
+#pragma unroll
+    for (int c = 0; c < CPT; c++)
+      if (col0 + c < dv && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col0 + c] = S[r][c];
 }
 
 }  // namespace dnseq
