@@ -87,6 +87,7 @@ struct dn_seq_model {
   CUtensorMap tm_loop_in, x_xg[2];    // x_xg: the tokens' rows sorted by expert [pairs, W], 64- and 128-row boxes
   bool tm_loop_ok = false, x_xg_ok = false;
   void* xg = nullptr;
+  float* attn_part = nullptr;         // partials of split attention rows [AT_SPLIT_ROWS][heads][AT_MAX_SPLITS][2 + vdim padded]
   XMaps x_cat, x_xm[SHIFT_MAX];
   size_t esz = 2;
   int S1 = 1, MB = 0, max_pages = 0;
@@ -193,7 +194,7 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   cudaDeviceSynchronize();
   void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
                   m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err, m->y2, m->x0, m->dz, m->rwt,
-                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles, m->xg};
+                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles, m->xg, m->attn_part};
   for (void* p : ptrs) if (p) cudaFree(p);
   for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
   if (m->lg_buf) cudaFree(m->lg_buf);
@@ -366,6 +367,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   DA(m->qn, MB * mdq * 4); DA(m->kn, MB * mdq * 4); DA(m->vv, MB * mo * 4); DA(m->od, MB * mo * 4);
   DA(m->beta, MB * mh * 4); DA(m->decay, MB * mh * 4);
   DA(m->y2, MB * W * 4); DA(m->dz, MB * mdq * 4); DA(m->lr, MB * mrank * e);
+  DA(m->attn_part, (size_t)AT_SPLIT_ROWS * mh * AT_MAX_SPLITS * (2 + 256) * 4);
   if (looped) { DA(m->x0, MB * W * 4); DA(m->cat, MB * 2 * W * e); }
   if (any_wkv) DA(m->xm, (size_t)SHIFT_MAX * MB * W * e);
   if (mpairs > 0) {
@@ -650,15 +652,16 @@ static cudaError_t gemm_tc_grouped(const CUtensorMap& x, const dn::TcParams& p, 
   return cudaGetLastError();
 }
 
-// the expert products of a routed feed-forward: h [N, W] -> m->y [N, W] (routed sum), m->y2 (shared expert, if any)
+// the expert products of a routed feed-forward: h [N, W] -> m->y [N, W] (routed sum), m->y2 (shared expert, if any);
+// fused: the sum of both goes through the norm after the sublayer into the plain residual in the combining kernel
 template <class T>
-static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
+static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, cudaStream_t s) {
   const dn_seq_layer_cfg& lc = l.c;
   const int W = m->cfg.width, E = lc.experts, top = lc.top, P = N * top;
   auto w = [&](int i) { return (const T*)l.w[i]; };
   auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
   CK(mark(m, DN_SEQ_PH_ROUTER, s));
-  CK(launch(k_router<T>, dim3(N), dim3(128), (size_t)E * 4, s, (const T*)m->h, w(DN_SQ_ROUTER), w(DN_SQ_ROUTER_B), W, E, top, m->ridx, m->rwt, m->rpos));
+  CK(launch(k_router<T>, dim3(N), dim3(32 * std::min(32, std::max(4, E))), (size_t)E * 4, s, (const T*)m->h, w(DN_SQ_ROUTER), w(DN_SQ_ROUTER_B), W, E, top, m->ridx, m->rwt, m->rpos));
   if (N <= 8) {
     CK(mark(m, DN_SEQ_PH_MOE_UP, s));
     CK(launch(k_moe_rows<T, true>, dim3((lc.ff + 7) / 8, P), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, (const int32_t*)m->ridx, top,
@@ -696,7 +699,6 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
       CK(launch(k_moe_tiles<T, false>, dim3((W + 63) / 64, mt), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, pl, m->eo, W, lc.ff, 0.f));
     }
   }
-  CK(launch(k_moe_combine, dim3((unsigned)(((size_t)N * W + 255) / 256)), dim3(256), 0, s, (const float*)m->eo, (const float*)m->rwt, (const int32_t*)m->rpos, N, W, top, m->y));
   if (lc.shared_ff > 0) {
     CK(mark(m, DN_SEQ_PH_FF_UP, s));
     CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_SH_GATE], l.w[DN_SQ_SH_UP], m->act, N, lc.shared_ff, W, false, ACT_CGLU,
@@ -704,6 +706,9 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, cudaStream_t s) {
     CK(mark(m, DN_SEQ_PH_FF_DOWN, s));
     CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_SH_DOWN], nullptr, m->y2, N, W, lc.shared_ff, true, 0, LinMaps{wm(DN_SQ_SH_DOWN), nullptr, &l.x_act}));
   }
+  CK(mark(m, DN_SEQ_PH_WRITE_BACK, s));
+  CK(launch(k_moe_combine<T>, dim3((unsigned)(((size_t)N * W + 255) / 256)), dim3(256), 0, s, (const float*)m->eo, (const float*)m->rwt, (const int32_t*)m->rpos, N, W, top,
+            m->y, fused ? m->xs : (float*)nullptr, lc.shared_ff > 0 ? (const float*)m->y2 : (const float*)nullptr, w(DN_SQ_POST2), w(DN_SQ_POST2_B), w(DN_SQ_POST2_ALPHA)));
   return DN_OK;
 }
 
@@ -820,10 +825,14 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       PH(DN_SEQ_PH_ATTN);
       if (attn_tiles_ok<T>(lc, b))
         CK(attn_tiles(s, b, (const bf16*)m->qb, (const bf16*)m->kpool[run.kv_index], (const bf16*)m->vpool[run.kv_index], lc, ex, (bf16*)m->mo));
-      else
-        CK(launch(k_attn<T>, dim3(N, lc.heads), dim3(AT_WARPS * 32), (size_t)(((lc.dim + 3) & ~3) + AT_WARPS * (2 + (lc.vdim + 31) / 32 * 32)) * 4, s, b,
+      else {
+        // a small step (decode): long rows are split over up to AT_MAX_SPLITS blocks, joined by k_attn_merge
+        const int Z = N <= AT_SPLIT_ROWS ? AT_MAX_SPLITS : 1;
+        CK(launch(k_attn<T>, dim3(N, lc.heads, Z), dim3(AT_WARPS * 32), (size_t)(((lc.dim + 3) & ~3) + AT_WARPS * (2 + (lc.vdim + 31) / 32 * 32)) * 4, s, b,
                   (const T*)m->qb, (const T*)m->kpool[run.kv_index],
-                  (const T*)m->vpool[run.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, ex, (T*)m->mo));
+                  (const T*)m->vpool[run.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, ex, (T*)m->mo, m->attn_part));
+        if (Z > 1) CK(launch(k_attn_merge<T>, dim3(N, lc.heads), dim3(128), 0, s, b, lc.heads, lc.vdim, lc.chunk, Z, ex, (const float*)m->attn_part, (T*)m->mo));
+      }
     } else if (lc.mixer == DN_MIX_DELTA) {
       if (!few) {
         CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));
@@ -920,10 +929,10 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
                 w(DN_SQ_NORM2_B), dyt ? w(DN_SQ_NORM2_ALPHA) : (const T*)nullptr));
       if (lc.mlp_kind == DN_MLP_MOE) {
-        const int rc = moe_ff<T>(m, l, N, s);
+        const bool fused = c.post_norm && S <= 0;
+        const int rc = moe_ff<T>(m, l, N, fused, s);
         if (rc != DN_OK) return rc;
-        PH(DN_SEQ_PH_WRITE_BACK);
-        CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, lc.shared_ff > 0 ? (const float*)m->y2 : nullptr, 1.f));
+        if (!fused) CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, lc.shared_ff > 0 ? (const float*)m->y2 : nullptr, 1.f));
       } else {
         PH(DN_SEQ_PH_FF_UP);
         CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, ACT_GEGLU, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));

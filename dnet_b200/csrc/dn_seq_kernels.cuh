@@ -553,7 +553,14 @@ struct AttnExtra {
   const void* sink;
   const float* gate;
 };
+// Long rows of a small step are split over gridDim.z blocks: a row that sees n keys uses ceil(n / AT_SPLIT_KEYS) of
+// them (at most gridDim.z), split z taking every nz-th group of AT_WARPS tiles; each writes its partial (maximum,
+// sum, output) to scratch and k_attn_merge joins them in the order of z.  The split depends on the row's own
+// position only.
+constexpr int AT_MAX_SPLITS = 16, AT_SPLIT_ROWS = 64;
 constexpr int AT_WARPS = 16;
+constexpr int AT_SPLIT_KEYS = AT_WARPS * 32;
+__device__ __forceinline__ int attn_splits(int keys, int zmax) { return min(zmax, max(1, (keys + AT_SPLIT_KEYS - 1) / AT_SPLIT_KEYS)); }
 template <class T>
 __device__ __forceinline__ void ld_vals(float (&v)[8], const T* p, int cnt, bool vec) {
   if (vec) {
@@ -579,7 +586,7 @@ __device__ __forceinline__ void ld_vals(float (&v)[8], const T* p, int cnt, bool
 template <class T>
 __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __restrict__ q, const T* __restrict__ kpool,
                                                         const T* __restrict__ vpool, int H, int G, int dk, int dv, int chunk, float scale,
-                                                        AttnExtra ex, T* __restrict__ out) {
+                                                        AttnExtra ex, T* __restrict__ out, float* __restrict__ part_g) {
   extern __shared__ __align__(16) float sm[];
   constexpr int V = 16 / (int)sizeof(T);
   const int VPL = (dv + 31) / 32, dvp = VPL * 32;
@@ -588,6 +595,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = h / (H / G), slot = b.slot[n], p = b.pos[n];
   const int lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  const int nz = attn_splits(p - lo + 1, (int)gridDim.z), z = blockIdx.z;
+  if (z >= nz) return;
   const int Ck = G * dk, Cv = G * dv;
   for (int d = threadIdx.x; d < dk; d += blockDim.x) qs[d] = ldf(q + ((size_t)n * H + h) * dk + d);
   __syncthreads();
@@ -598,7 +607,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.f;
-  for (int j0 = lo + warp * 32; j0 <= p; j0 += AT_WARPS * 32) {
+  for (int j0 = lo + (z * AT_WARPS + warp) * 32; j0 <= p; j0 += nz * AT_WARPS * 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
     if (j <= p) {
@@ -643,17 +652,46 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   for (int i = 0; i < 8; i++)
     if (i < VPL) mine[2 + lane * VPL + i] = acc[i];
   __syncthreads();
-  const float snk = ex.sink ? ldf((const T*)ex.sink + h) : -INFINITY;
+  const bool split = nz > 1;      // the sink and the gate then wait for the merge
+  const float snk = (ex.sink && !split) ? ldf((const T*)ex.sink + h) : -INFINITY;
   const float og = ex.gate ? sigmoid_f(ex.gate[(size_t)n * H + h]) : 1.f;
+  float* pg = split ? part_g + (((size_t)n * H + h) * gridDim.z + z) * (2 + dvp) : nullptr;
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float M = snk;
     for (int w = 0; w < AT_WARPS; w++) M = fmaxf(M, part[(size_t)w * (2 + dvp)]);
-    float L = ex.sink ? expf(snk - M) : 0.f, a = 0.f;
+    float L = (ex.sink && !split) ? expf(snk - M) : 0.f, a = 0.f;
     for (int w = 0; w < AT_WARPS; w++) {
       const float* pw = part + (size_t)w * (2 + dvp);
       const float f = expf(pw[0] - M);     // a warp that saw no tile has maximum -inf and weight 0
       L += pw[1] * f;
       a += pw[2 + d] * f;
+    }
+    if (split) {
+      pg[2 + d] = a;
+      if (d == 0) { pg[0] = M; pg[1] = L; }
+    } else stf(out + ((size_t)n * H + h) * dv + d, a / L * og);
+  }
+}
+// joins the partials of the rows that k_attn split (rows with one split are complete already); grid (N, H, 1)
+template <class T>
+__global__ void k_attn_merge(Batch b, int H, int dv, int chunk, int zmax, AttnExtra ex, const float* __restrict__ part_g, T* __restrict__ out) {
+  const int n = blockIdx.x, h = blockIdx.y, p = b.pos[n];
+  const int lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  const int nz = attn_splits(p - lo + 1, zmax);
+  if (nz <= 1) return;
+  const int dvp = (dv + 31) / 32 * 32;
+  const float* pg = part_g + ((size_t)n * H + h) * zmax * (2 + dvp);
+  const float snk = ex.sink ? ldf((const T*)ex.sink + h) : -INFINITY;
+  const float og = ex.gate ? sigmoid_f(ex.gate[(size_t)n * H + h]) : 1.f;
+  float M = snk;
+  for (int z = 0; z < nz; z++) M = fmaxf(M, pg[(size_t)z * (2 + dvp)]);
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float L = ex.sink ? expf(snk - M) : 0.f, a = 0.f;
+    for (int z = 0; z < nz; z++) {
+      const float* pz = pg + (size_t)z * (2 + dvp);
+      const float f = expf(pz[0] - M);
+      L += pz[1] * f;
+      a += pz[2 + d] * f;
     }
     stf(out + ((size_t)n * H + h) * dv + d, a / L * og);
   }

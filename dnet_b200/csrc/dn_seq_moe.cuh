@@ -14,7 +14,7 @@ namespace dnseq {
 
 // one block per token: logits, top-k (ties: the lower index), softmax over the chosen; pos[p] = p
 template <class T>
-__global__ void __launch_bounds__(128) k_router(const T* __restrict__ h, const T* __restrict__ Wr, const T* __restrict__ br, int W, int E,
+__global__ void __launch_bounds__(1024) k_router(const T* __restrict__ h, const T* __restrict__ Wr, const T* __restrict__ br, int W, int E,
                                                 int top, int32_t* __restrict__ idx, float* __restrict__ wt, int32_t* __restrict__ pos) {
   extern __shared__ float zl[];      // [E]
   const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -22,7 +22,18 @@ __global__ void __launch_bounds__(128) k_router(const T* __restrict__ h, const T
   for (int e = warp; e < E; e += nw) {
     const T* wr = Wr + (size_t)e * W;
     float a = 0.f;
-    for (int c = lane; c < W; c += 32) a = fmaf(ldf(x + c), ldf(wr + c), a);
+    constexpr int V = Vec16<T>::n;
+    if (W % V == 0 && ((((uintptr_t)h | (uintptr_t)Wr) & 15) == 0)) {      // rows start on 16-byte boundaries
+      for (int c = lane * V; c < W; c += 32 * V) {
+        T xv[V], wv[V];
+        *reinterpret_cast<uint4*>(xv) = *reinterpret_cast<const uint4*>(x + c);
+        *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(wr + c);
+#pragma unroll
+        for (int j = 0; j < V; j++) a = fmaf(ldf(xv + j), ldf(wv + j), a);
+      }
+    } else {
+      for (int c = lane; c < W; c += 32) a = fmaf(ldf(x + c), ldf(wr + c), a);
+    }
     a = warp_sum(a);
     if (lane == 0) zl[e] = a + (br ? ldf(br + e) : 0.f);
   }
@@ -182,16 +193,21 @@ __global__ void k_moe_gather(const T* __restrict__ h, const int32_t* __restrict_
   }
 }
 
-// y[n] = sum_j wt[n, j] out[pos[n, j]], the pairs of a token in the order of its choices
+// y[n] = sum_j wt[n, j] out[pos[n, j]], the pairs of a token in the order of its choices.  With x: the sum (plus the
+// shared expert's output y2, if any) goes through the dynamic-tanh norm after the sublayer straight into the plain
+// residual, x[n] += dyt(y[n] + y2[n]), and y is not written.
+template <class T>
 __global__ void k_moe_combine(const float* __restrict__ eo, const float* __restrict__ wt, const int32_t* __restrict__ pos, int N, int W, int top,
-                              float* __restrict__ y) {
+                              float* __restrict__ y, float* __restrict__ x, const float* __restrict__ y2, const T* __restrict__ nw,
+                              const T* __restrict__ nb, const T* __restrict__ nalpha) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)N * W) return;
   const size_t n = i / W;
   const int c = (int)(i % W);
   float a = 0.f;
   for (int j = 0; j < top; j++) a = fmaf(wt[n * top + j], eo[(size_t)pos[n * top + j] * W + c], a);
-  y[i] = a;
+  if (x) x[i] += dyt_f(a + (y2 ? y2[i] : 0.f), ldf(nalpha), nw, nb, c);
+  else y[i] = a;
 }
 
 }  // namespace dnseq
