@@ -445,3 +445,76 @@ def test_command_lines_on_a_checkpoint_folder(tmp_path):
     assert err(got[0], ref[[49]]) < TOL["float32"]
     assert err(got[1], torch.cat([ref[[50, 51]], fo.forward(cfg, w, t[:9])[[8]]])) < TOL["float32"]
     assert err(got[2], ref[[69]]) < TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_allow_no_wide_loads(dtype):
+    """width, head, expert and vocabulary sizes that are multiples of neither 4 nor 8: the scalar forms of every kernel"""
+    moe = {"kind": "moe", "router": {"experts": 5, "top": 3}, "expert": {"ff": 30, "limit": 1.1}, "shared": {"ff": 45, "limit": 2.2}}
+    cfg = config([wkv(moe, heads=2, dim=10), par(moe, left={"heads": 3, "kv_heads": 3, "dim": 6, "vdim": 9}, right={"heads": 1, "dim": 7, "vdim": 5}),
+                  wkv(None, heads=1, dim=9)], loop=(1, 3, 2), width=50, vocab=77)
+    t = toks(120, vocab=77, seed=160)
+    with Rig(cfg, dtype, rank=3) as rig:
+        ref = rig.oracle(t)
+        e = err16 if dtype == "bfloat16" else err
+        assert e(run_schedule(rig, t, [120]), ref) < TOL[dtype]
+        assert e(run_schedule(rig, t, [70, 2, 20]), ref) < TOL[dtype]
+
+
+def test_long_rows_split_over_blocks_in_decoding():
+    """decoding past 512, 1024 and 1536 keys: a row's attention is then computed by 2, 3 and 4 blocks and joined"""
+    cfg = config([par(left={"heads": 2, "kv_heads": 1, "dim": 16, "vdim": 40, "scale": 1.5, "softcap": 4.0})])
+    t = toks(1560, seed=165)
+    with Rig(cfg, "float32", max_tokens=1600, max_batch_tokens=1600) as rig:
+        ref = rig.oracle(t)
+        got = []
+        for first, n in ((508, 8), (1020, 8), (1532, 8)):
+            lg = run_schedule(rig, t[:first + n], [first])
+            got.append((lg[first:], ref[first:first + n]))
+        for a, b in got:
+            assert err(a, b) < TOL["float32"]
+
+
+def test_served_by_the_shard_runtime():
+    """load_model_core finds the class by the config's architecture and serves it with the batched policy: frames of
+    tokens in, sampled tokens out, chunked prompts, slots and pages returned at release"""
+    import queue
+
+    from dnet_b200.shard.models import ShardLoadModelRequest
+    from dnet_b200.shard.policies.batched import BatchedStepPolicy
+    from dnet_b200.shard.runtime import ShardRuntime
+    from dnet_b200.utils.model import HostDictSource
+    from tests.helpers import ring_generate, token_message
+
+    w = decisive(fo.random_weights(FULL, 21))
+    n = len(FULL["layers"])
+    rt = ShardRuntime(shard_id="s0", queue_size=64)
+    rt.kv_cache_config.max_tokens = 256
+    src = HostDictSource({k: v.to(torch.bfloat16) for k, v in w.items()}, FULL)
+    rt.load_model_core(ShardLoadModelRequest(model_path=src, total_layers=n, layers=list(range(n)), window_size=n, residency_size=n, kv_bits="fp16"))
+    try:
+        assert isinstance(rt.policy, BatchedStepPolicy)
+
+        def oracle_greedy(prompt, got):
+            seq = list(prompt)
+            for tok in got:
+                lg = fo.forward(FULL, w, seq)[-1]
+                top = torch.topk(lg, 2).values
+                if float(top[0] - top[1]) > 5e-2 * float(lg.std()):        # bf16 serving: only clear winners are compared
+                    assert tok == int(lg.argmax())
+                seq.append(tok)
+
+        a, b = toks(45, seed=180), toks(70, seed=181)
+        out_a = [t for t, _, _ in ring_generate([rt], "na", a, 5)]
+        oracle_greedy(a, out_a)
+        for part in (b[:30], b[30:64]):
+            rt.policy.process(token_message(rt, "nb", part, more=True))
+            with pytest.raises(queue.Empty):
+                rt.activation_send_queue.get_nowait()
+        out_b = [t for t, _, _ in ring_generate([rt], "nb", b[64:], 4)]
+        oracle_greedy(b, out_b)
+        rt.release_nonce("na")
+        rt.release_nonce_deferred("nb")
+        assert rt.model.free_pages == rt.model.pool_pages
+    finally:
+        assert rt.unload_model_core().success
