@@ -19,6 +19,7 @@
 //                residual or feed fp32 gates)
 //   EPI_GEGLU  : two weight tiles like EPI_SWIGLU; y = T(gelu_tanh(acc_g) * acc_u), the activation and the product
 //                in fp32 with one rounding                     -> Y[t][n]
+//   EPI_TANH   : y = T(tanh(acc))                              -> Y[t][n]
 //   EPI_CGLU   : two weight tiles; g = min(acc_g, limit), u = clamp(acc_u, -limit, limit), y = T(g sigmoid(1.702 g) (u + 1))
 //
 // GROUPED: one launch over many weight matrices of one shape (routed experts).  The token rows are sorted by matrix
@@ -31,7 +32,7 @@
 
 namespace dn {
 
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_GEGLU = 4, EPI_CGLU = 5 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_GEGLU = 4, EPI_CGLU = 5, EPI_TANH = 6 };
 __host__ __device__ constexpr bool epi_two_weights(int epi) { return epi == EPI_SWIGLU || epi == EPI_GEGLU || epi == EPI_CGLU; }
 
 constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
@@ -229,6 +230,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
               if (EPI == EPI_GEGLU) {
                 const float g = v[j];
                 y = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * v2[j];
+              } else if (EPI == EPI_TANH) {
+                y = tanhf(v[j]);
               } else if (EPI == EPI_CGLU) {
                 const float g = fminf(v[j], p.limit), u = fminf(fmaxf(v2[j], -p.limit), p.limit);
                 y = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);

@@ -576,11 +576,13 @@ struct LinMaps { const CUtensorMap* w; const CUtensorMap* w2; const XMaps* x; };
 template <class T>
 static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32,
                           int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}, float alim = 0.f) {
-  if (std::is_same<T, bf16>::value && N >= 16 && O >= 32 && tm.w && tm.x && tm.x->ok && (act == ACT_NONE || ((act == ACT_GEGLU || act == ACT_CGLU) && tm.w2))) {
+  // (a weight of fewer than 128 rows fills part of a tile: still far ahead of the CUDA-core tiles once K is in the thousands)
+  if (std::is_same<T, bf16>::value && N >= 16 && O >= 16 && tm.w && tm.x && tm.x->ok && (act == ACT_NONE || act == ACT_TANH || ((act == ACT_GEGLU || act == ACT_CGLU) && tm.w2))) {
     dn::TcParams p;
     memset(&p, 0, sizeof(p));
     p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err; p.limit = alim;
     if (act == ACT_CGLU) return gemm_tc<dn::EPI_CGLU>(*tm.w, *tm.w2, *tm.x, p, s);
+    if (act == ACT_TANH) return gemm_tc<dn::EPI_TANH>(*tm.w, *tm.w, *tm.x, p, s);
     if (act) return gemm_tc<dn::EPI_GEGLU>(*tm.w, *tm.w2, *tm.x, p, s);
     if (out32) return gemm_tc<dn::EPI_STORE_F32>(*tm.w, *tm.w, *tm.x, p, s);
     return gemm_tc<dn::EPI_STORE>(*tm.w, *tm.w, *tm.x, p, s);
@@ -722,16 +724,16 @@ static void recur_shape(int dk, int* R, int* P) {
 static int decay_rule(dn_seq_model* m, const Batch& b, int mode, int H, int dk, int dv, const void* bonus, float* st, cudaStream_t s) {
   int R, P;
   recur_shape(dk, &R, &P);
-  dim3 grid(b.E * H, (dv + 31) / 32);
-  const int per = 3 * P * (R + 4) + 32;
+  // columns a block: 16 where that still fills whole warps (twice the blocks, half the shared-memory reads a block and token)
+  const int cols = P >= 2 ? 16 : 32;
+  dim3 grid(b.E * H, (dv + cols - 1) / cols);
+  const int per = 3 * P * (R + 4) + cols;
   int TB = std::max(1, std::min(16, 4500 / per));
   if (TB >= 4) TB &= ~3;      // whole groups of the kernel's four-token batches
   const size_t dsm = (size_t)2 * TB * per * 4;
-#define DR(Rv, Pv, Cp) if (R == Rv && P == Pv) CK(launch(k_decay_rule<Rv, Pv, Cp>, grid, dim3((32 / Cp) * Pv), dsm, s, mode, b, H, dk, dv, TB, (const float*)m->qn, \
+#define DR(Rv, Pv, Cv_) if (R == Rv && P == Pv) CK(launch(k_decay_rule<Rv, Pv, Cv_>, grid, dim3(Cv_ * Pv), dsm, s, mode, b, H, dk, dv, TB, (const float*)m->qn, \
                          (const float*)m->kn, (const float*)m->vv, (const float*)m->dz, bonus, m->esz == 4 ? 1 : 0, st, m->delta_stride, m->od))
-  // one column a thread: 2 and 4 columns (fewer shared-memory reads, fewer warps) measured slower, the token chain has
-  // too few warps left to hide its latency
-  DR(8, 1, 1); DR(8, 2, 1); DR(8, 4, 1); DR(8, 8, 1); DR(16, 8, 1); DR(16, 16, 1); DR(16, 32, 1); DR(32, 32, 1);
+  DR(8, 1, 32); DR(8, 2, 16); DR(8, 4, 16); DR(8, 8, 16); DR(16, 8, 16); DR(16, 16, 16); DR(16, 32, 16); DR(32, 32, 16);
 #undef DR
   return DN_OK;
 }
@@ -876,7 +878,7 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
         CK(linear<T>(m, s, xm + 2 * xs_, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_xm[2]}));
         CK(linear<T>(m, s, xm + 3 * xs_, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0, LinMaps{wm(DN_SQ_G), nullptr, &m->x_xm[3]}));
       }
-      CK(linear<T>(m, s, xm + 4 * xs_, l.w[DN_SQ_DECAY1], nullptr, m->lr, N, lc.rank, W, false, ACT_TANH, LinMaps{nullptr, nullptr, nullptr}));
+      CK(linear<T>(m, s, xm + 4 * xs_, l.w[DN_SQ_DECAY1], nullptr, m->lr, N, lc.rank, W, false, ACT_TANH, LinMaps{wm(DN_SQ_DECAY1), nullptr, &m->x_xm[4]}));
       CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_DECAY2], nullptr, m->dz, N, l.Cq, lc.rank, true, 0, LinMaps{wm(DN_SQ_DECAY2), nullptr, &l.x_lr}));
       PH(DN_SEQ_PH_RECUR_PREP);
       CK(launch(k_decay_prep<T>, dim3(N), dim3(256), 0, s, RECUR_BONUS, N, l.Cq, l.Cv, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_DECAY_B),

@@ -57,43 +57,42 @@ __global__ void k_decay_prep(int mode, int N, int C, int Cv, const T* __restrict
   for (int c = threadIdx.x; c < Cv; c += blockDim.x) vv[(size_t)n * Cv + c] = ldf(Uv + (size_t)n * Cv + c);
 }
 
-// The recurrence, token by token.  Columns of M are independent: a block owns 32 columns of one (entry, head); P
-// adjacent lanes share a group of CPT columns, each lane holding R consecutive rows (P R >= dk) of those columns in
-// registers (R x CPT state values a thread), so a token's k, q and decay are read once for CPT columns.  State
-// [slot][head][dk][dv] fp32, read once and written once per step.  A token's k, q, decay and the block's 32 values
+// The recurrence, token by token.  Columns of M are independent: a block owns COLS columns of one (entry, head); P
+// adjacent lanes share a column, each holding R consecutive rows (P R >= dk) in registers.  State
+// [slot][head][dk][dv] fp32, read once and written once per step.  A token's k, q, decay and the block's COLS values
 // come through shared memory in tiles of TB tokens, copied asynchronously one tile ahead; k, q and the decay lie
-// there as P runs of R values, each run padded by 4 floats (the 16-byte reads of a group's P lanes fall into
+// there as P runs of R values, each run padded by 4 floats (the 16-byte reads of a column's P lanes fall into
 // different banks); rows from dk up are zero.  The read-out sums a thread's rows in ascending order, then the lanes
-// of a group pairwise: an order fixed by (dk, P), whatever the tile size or the cut of a prompt.  U tokens are
-// taken at a time: their state updates run back to back and their read-outs are reduced together (U x CPT
-// independent shuffle chains in flight).
-template <int R, int P, int CPT>
-__global__ void __launch_bounds__((32 / CPT) * P) k_decay_rule(int mode, Batch b, int H, int dk, int dv, int TB, const float* __restrict__ qn,
-                                                               const float* __restrict__ kn, const float* __restrict__ vv,
-                                                               const float* __restrict__ decay, const void* __restrict__ bonus, int bonus_f32,
-                                                               float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
-  static_assert((32 / CPT) * P >= 32 && 32 % CPT == 0, "whole warps");
+// of a column pairwise: an order fixed by (dk, P), whatever the tile size or the cut of a prompt.  Four tokens are
+// taken at a time: their state updates run back to back and their read-outs are reduced together (four independent
+// shuffle chains in flight).
+template <int R, int P, int COLS>
+__global__ void __launch_bounds__(COLS * P) k_decay_rule(int mode, Batch b, int H, int dk, int dv, int TB, const float* __restrict__ qn,
+                                                         const float* __restrict__ kn, const float* __restrict__ vv,
+                                                         const float* __restrict__ decay, const void* __restrict__ bonus, int bonus_f32,
+                                                         float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+  static_assert(COLS * P >= 32 && (COLS * P) % 32 == 0 && COLS % 4 == 0 && COLS <= 32, "whole warps, 16-byte rows");
   extern __shared__ __align__(16) float dsm[];      // 2 x TB x per
   constexpr int KP = P * (R + 4);
-  constexpr int per = 3 * KP + 32;                  // k q decay v[32]
-  constexpr int U = CPT >= 4 ? 2 : 4;
+  constexpr int per = 3 * KP + COLS;                // k q decay v[COLS]
+  constexpr int U = 4;
   const int e = blockIdx.x / H, h = blockIdx.x % H;
-  const int part = threadIdx.x % P, colg = threadIdx.x / P, col0 = blockIdx.y * 32 + colg * CPT;
+  const int part = threadIdx.x % P, colb = threadIdx.x / P, col = blockIdx.y * COLS + colb;
   const int s0 = b.ent_start[e], s1 = b.ent_start[e + 1];
+  const bool live = col < dv;
   float* Sg = state + (size_t)b.ent_slot[e] * slot_stride + (size_t)h * dk * dv;
   const int r0 = part * R;
-  float S[R][CPT], u[R];
+  float S[R], u[R];
 #pragma unroll
   for (int r = 0; r < R; r++) {
-#pragma unroll
-    for (int c = 0; c < CPT; c++) S[r][c] = (col0 + c < dv && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col0 + c] : 0.f;
+    S[r] = (live && r0 + r < dk) ? Sg[(size_t)(r0 + r) * dv + col] : 0.f;
     u[r] = 0.f;
     if (mode == RECUR_BONUS && r0 + r < dk)
       u[r] = bonus_f32 ? ((const float*)bonus)[(size_t)h * dk + r0 + r] : __bfloat162float(((const bf16*)bonus)[(size_t)h * dk + r0 + r]);
   }
   const int C = H * dk, Cv = H * dv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int nwarp = (32 / CPT) * P / 32;
+  constexpr int nwarp = COLS * P / 32;
   auto stage = [&](int buf, int n0) {
     const int cnt = min(TB, s1 - n0);
     for (int t = warp; t < cnt; t += nwarp) {
@@ -105,9 +104,11 @@ __global__ void __launch_bounds__((32 / CPT) * P) k_decay_rule(int mode, Batch b
         if (c < dk) { cp_async4(dst + idx, kn + base + c); cp_async4(dst + KP + idx, qn + base + c); cp_async4(dst + 2 * KP + idx, decay + base + c); }
         else dst[idx] = dst[KP + idx] = dst[2 * KP + idx] = 0.f;
       }
-      const int vc = blockIdx.y * 32 + lane;
-      if (vc < dv) cp_async4(dst + 3 * KP + lane, vv + (size_t)n * Cv + h * dv + vc);
-      else dst[3 * KP + lane] = 0.f;
+      if (lane < COLS) {
+        const int vc = blockIdx.y * COLS + lane;
+        if (vc < dv) cp_async4(dst + 3 * KP + lane, vv + (size_t)n * Cv + h * dv + vc);
+        else dst[3 * KP + lane] = 0.f;
+      }
     }
     cp_async_commit();
   };
@@ -119,36 +120,30 @@ __global__ void __launch_bounds__((32 / CPT) * P) k_decay_rule(int mode, Batch b
     __syncthreads();
     const int cnt = min(TB, s1 - n0);
     for (int t0 = 0; t0 < cnt; t0 += U) {
-      float od[U][CPT];
+      float od[U];
 #pragma unroll
       for (int uu = 0; uu < U; uu++) {
-#pragma unroll
-        for (int c = 0; c < CPT; c++) od[uu][c] = 0.f;
+        od[uu] = 0.f;
         if (t0 + uu < cnt) {
           const float* in = dsm + ((size_t)buf * TB + t0 + uu) * per;
           const float4* k4 = reinterpret_cast<const float4*>(in + part * (R + 4));
           const float4* q4 = reinterpret_cast<const float4*>(in + KP + part * (R + 4));
           const float4* d4 = reinterpret_cast<const float4*>(in + 2 * KP + part * (R + 4));
-          float v[CPT];
-#pragma unroll
-          for (int c = 0; c < CPT; c++) v[c] = in[3 * KP + colg * CPT + c];
+          const float v = in[3 * KP + colb];
 #pragma unroll
           for (int j = 0; j < R / 4; j++) {
             const float4 kv = k4[j], qv = q4[j], dv4 = d4[j];
             const float kk[4] = {kv.x, kv.y, kv.z, kv.w}, qq[4] = {qv.x, qv.y, qv.z, qv.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-#pragma unroll
-              for (int c = 0; c < CPT; c++) {
-                const float kvp = kk[i] * v[c];
-                float& Sr = S[4 * j + i][c];
-                if (mode == RECUR_BONUS) {
-                  od[uu][c] = fmaf(fmaf(u[4 * j + i], kvp, Sr), qq[i], od[uu][c]);
-                  Sr = fmaf(dd[i], Sr, kvp);
-                } else {
-                  Sr = fmaf(dd[i], Sr, kvp);
-                  od[uu][c] = fmaf(Sr, qq[i], od[uu][c]);
-                }
+              const float kvp = kk[i] * v;
+              float& Sr = S[4 * j + i];
+              if (mode == RECUR_BONUS) {
+                od[uu] = fmaf(fmaf(u[4 * j + i], kvp, Sr), qq[i], od[uu]);
+                Sr = fmaf(dd[i], Sr, kvp);
+              } else {
+                Sr = fmaf(dd[i], Sr, kvp);
+                od[uu] = fmaf(Sr, qq[i], od[uu]);
               }
             }
           }
@@ -157,27 +152,19 @@ __global__ void __launch_bounds__((32 / CPT) * P) k_decay_rule(int mode, Batch b
 #pragma unroll
       for (int x = 1; x < P; x <<= 1) {
 #pragma unroll
-        for (int uu = 0; uu < U; uu++)
-#pragma unroll
-          for (int c = 0; c < CPT; c++) od[uu][c] += __shfl_xor_sync(0xffffffffu, od[uu][c], x);
+        for (int uu = 0; uu < U; uu++) od[uu] += __shfl_xor_sync(0xffffffffu, od[uu], x);
       }
-      if (part == 0) {
+      if (live && part == 0) {
 #pragma unroll
         for (int uu = 0; uu < U; uu++)
-          if (t0 + uu < cnt) {
-#pragma unroll
-            for (int c = 0; c < CPT; c++)
-              if (col0 + c < dv) o[(size_t)(n0 + t0 + uu) * Cv + h * dv + col0 + c] = od[uu][c];
-          }
+          if (t0 + uu < cnt) o[(size_t)(n0 + t0 + uu) * Cv + h * dv + col] = od[uu];
       }
     }
     __syncthreads();      // the tile is read out before the copy after next lands in it
   }
 #pragma unroll
   for (int r = 0; r < R; r++)
-#pragma unroll
-    for (int c = 0; c < CPT; c++)
-      if (col0 + c < dv && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col0 + c] = S[r][c];
+    if (live && r0 + r < dk) Sg[(size_t)(r0 + r) * dv + col] = S[r];
 }
 
 }  // namespace dnseq

@@ -173,7 +173,7 @@ def test_full_model_whole_prompt(dtype):
 def test_sizes_on_the_tensor_core_products():
     """width and projection sizes in multiples of 64: bf16 prompt portions take the tcgen05 products and the MMA attention"""
     moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 128, "limit": 2.5}, "shared": {"ff": 192, "limit": 1.0}}
-    cfg = config([wkv(moe, heads=4, dim=32), par(moe, left={"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32}, right={"heads": 2, "dim": 32, "vdim": 64})],
+    cfg = config([wkv(moe, heads=4, dim=32), par(moe, left={"heads": 16, "kv_heads": 2, "dim": 16, "vdim": 8}, right={"heads": 2, "dim": 32, "vdim": 64})],
                  loop=(0, 2, 2), width=128, vocab=192)
     t = toks(300, vocab=192, seed=6)
     with Rig(cfg, "bfloat16", rank=64) as rig:
