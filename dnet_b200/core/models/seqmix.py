@@ -316,6 +316,8 @@ class SeqMixRingModel(BaseRingModel):
                 if strict:
                     raise ValueError(f"unexpected tensor {key}")
                 continue
+            if shape == () and t.numel() == 1:
+                t = t.reshape(())           # a scalar stored as [1]
             if tuple(t.shape) != shape:
                 raise ValueError(f"{key}: shape {tuple(t.shape)}, the config asks for {shape}")
             if not t.is_cuda or t.dtype != self.dtype or not t.is_contiguous():

@@ -664,13 +664,16 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, cudaStream_t 
   auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
   CK(mark(m, DN_SEQ_PH_ROUTER, s));
   CK(launch(k_router<T>, dim3(N), dim3(32 * std::min(32, std::max(4, E))), (size_t)E * 4, s, (const T*)m->h, w(DN_SQ_ROUTER), w(DN_SQ_ROUTER_B), W, E, top, m->ridx, m->rwt, m->rpos));
-  if (N <= 8) {
+  const bool few = N <= 8;
+  if (few) {      // the shared expert's rows ride in the same two launches
+    SharedExpert sh{l.w[DN_SQ_SH_GATE], l.w[DN_SQ_SH_UP], l.w[DN_SQ_SH_DOWN], lc.shared_ff, lc.shared_limit, m->act, m->y2};
+    const int rows = P + (lc.shared_ff > 0 ? N : 0);
     CK(mark(m, DN_SEQ_PH_MOE_UP, s));
-    CK(launch(k_moe_rows<T, true>, dim3((lc.ff + 7) / 8, P), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, (const int32_t*)m->ridx, top,
-              m->eact, lc.ff, W, lc.limit));
+    CK(launch(k_moe_rows<T, true>, dim3((std::max(lc.ff, lc.shared_ff) + 7) / 8, rows), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E,
+              (const int32_t*)m->ridx, top, m->eact, lc.ff, W, lc.limit, P, (const T*)m->h, sh));
     CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
-    CK(launch(k_moe_rows<T, false>, dim3((W + 7) / 8, P), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, (const int32_t*)m->ridx, top,
-              m->eo, W, lc.ff, 0.f));
+    CK(launch(k_moe_rows<T, false>, dim3((W + 7) / 8, rows), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, (const int32_t*)m->ridx, top,
+              m->eo, W, lc.ff, 0.f, P, (const T*)m->h, sh));
   } else {
     MoePlan pl{m->rpos, m->rtok, m->tiles, m->tiles + m->max_tiles, m->tiles + 2 * m->max_tiles, m->tiles + 3 * m->max_tiles};
     const int mt = std::min(m->max_tiles, P / MOE_ROWS + E + 1);
@@ -701,7 +704,7 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, cudaStream_t 
       CK(launch(k_moe_tiles<T, false>, dim3((W + 63) / 64, mt), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, pl, m->eo, W, lc.ff, 0.f));
     }
   }
-  if (lc.shared_ff > 0) {
+  if (lc.shared_ff > 0 && !few) {
     CK(mark(m, DN_SEQ_PH_FF_UP, s));
     CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_SH_GATE], l.w[DN_SQ_SH_UP], m->act, N, lc.shared_ff, W, false, ACT_CGLU,
                  LinMaps{wm(DN_SQ_SH_GATE), wm(DN_SQ_SH_UP), &m->x_h}, lc.shared_limit));
@@ -794,7 +797,7 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     memset(&sg, 0, sizeof(sg));
     auto add = [&](const void* x, int which, void* y, int rows, int o32) {
       if (rows <= 0) return;
-      sg.X[sg.n] = x; sg.W[sg.n] = l.w[which]; sg.Y[sg.n] = y; sg.O[sg.n] = rows; sg.out32[sg.n] = o32; sg.n++;
+      sg.X[sg.n] = x; sg.W[sg.n] = l.w[which]; sg.Y[sg.n] = y; sg.O[sg.n] = rows; sg.out32[sg.n] = o32; sg.act[sg.n] = ACT_NONE; sg.n++;
     };
     auto run_segs = [&]() {
       int blocks = 0;
@@ -867,22 +870,25 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       const size_t xs_ = (size_t)m->MB * W;
       T* xm = (T*)m->xm;
       CK(launch(k_shift_mix<T>, dim3(N), dim3(256), 0, s, (const T*)m->h, b, W, mu, (const T*)cst, m->conv_stride, xm, xs_));
-      CK(launch(k_shift_carry<T>, dim3((W + 255) / 256, b.E), dim3(256), 0, s, (const T*)m->h, b, W, cst, m->conv_stride));
-      if (few) {
+      ShiftCarry<T> carry{nullptr, cst, m->conv_stride, W, b.first, b.slot};
+      if (few) {      // one launch for all five projections (the decay's inner one with its tanh); the prep kernel carries the row
         add(xm, DN_SQ_Q, m->uq, l.Cq, 0); add(xm + xs_, DN_SQ_K, m->uk, l.Ck, 0); add(xm + 2 * xs_, DN_SQ_V, m->uv, l.Cv, 0);
-        add(xm + 3 * xs_, DN_SQ_G, m->gt, l.Co, 0);
+        add(xm + 3 * xs_, DN_SQ_G, m->gt, l.Co, 0); add(xm + 4 * xs_, DN_SQ_DECAY1, m->lr, lc.rank, 0);
+        sg.act[sg.n - 1] = ACT_TANH;
         CK(run_segs());
+        carry.h = (const T*)m->h;
       } else {
+        CK(launch(k_shift_carry<T>, dim3((W + 255) / 256, b.E), dim3(256), 0, s, (const T*)m->h, b, W, cst, m->conv_stride));
         CK(linear<T>(m, s, xm, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, W, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &m->x_xm[0]}));
         CK(linear<T>(m, s, xm + xs_, l.w[DN_SQ_K], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_K), nullptr, &m->x_xm[1]}));
         CK(linear<T>(m, s, xm + 2 * xs_, l.w[DN_SQ_V], nullptr, m->uv, N, l.Cv, W, false, 0, LinMaps{wm(DN_SQ_V), nullptr, &m->x_xm[2]}));
         CK(linear<T>(m, s, xm + 3 * xs_, l.w[DN_SQ_G], nullptr, m->gt, N, l.Co, W, false, 0, LinMaps{wm(DN_SQ_G), nullptr, &m->x_xm[3]}));
       }
-      CK(linear<T>(m, s, xm + 4 * xs_, l.w[DN_SQ_DECAY1], nullptr, m->lr, N, lc.rank, W, false, ACT_TANH, LinMaps{wm(DN_SQ_DECAY1), nullptr, &m->x_xm[4]}));
+      if (!few) CK(linear<T>(m, s, xm + 4 * xs_, l.w[DN_SQ_DECAY1], nullptr, m->lr, N, lc.rank, W, false, ACT_TANH, LinMaps{wm(DN_SQ_DECAY1), nullptr, &m->x_xm[4]}));
       CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_DECAY2], nullptr, m->dz, N, l.Cq, lc.rank, true, 0, LinMaps{wm(DN_SQ_DECAY2), nullptr, &l.x_lr}));
       PH(DN_SEQ_PH_RECUR_PREP);
       CK(launch(k_decay_prep<T>, dim3(N), dim3(256), 0, s, RECUR_BONUS, N, l.Cq, l.Cv, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_DECAY_B),
-                1.f, 1.f, m->qn, m->kn, m->vv, m->dz));
+                1.f, 1.f, m->qn, m->kn, m->vv, m->dz, carry));
       PH(DN_SEQ_PH_RECUR);
       { const int rc = decay_rule(m, b, RECUR_BONUS, lc.heads, lc.dim, lc.vdim, l.w[DN_SQ_BONUS], st, s); if (rc != DN_OK) return rc; }
       PH(DN_SEQ_PH_RECUR_OUT);
@@ -913,7 +919,7 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_DECAY2], nullptr, m->dz, N, l.Rc, lc.rank, true, 0, LinMaps{wm(DN_SQ_DECAY2), nullptr, &l.x_lr}));
       PH(DN_SEQ_PH_RECUR_PREP);
       CK(launch(k_decay_prep<T>, dim3(N), dim3(256), 0, s, RECUR_AFTER, N, l.Rc, l.Rv, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_DECAY_B),
-                1.f / sqrtf((float)lc.r_dim), lc.tau, m->qn, m->kn, m->vv, m->dz));
+                1.f / sqrtf((float)lc.r_dim), lc.tau, m->qn, m->kn, m->vv, m->dz, ShiftCarry<T>{nullptr, nullptr, 0, 0, nullptr, nullptr}));
       PH(DN_SEQ_PH_RECUR);
       { const int rc = decay_rule(m, b, RECUR_AFTER, lc.r_heads, lc.r_dim, lc.r_vdim, nullptr, st, s); if (rc != DN_OK) return rc; }
       PH(DN_SEQ_PH_RECUR_OUT);

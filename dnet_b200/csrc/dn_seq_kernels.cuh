@@ -404,6 +404,7 @@ struct LinSegs {
   void* Y[MAX_SEGS];
   int O[MAX_SEGS];
   int out32[MAX_SEGS];
+  int act[MAX_SEGS];         // ACT_NONE or ACT_TANH
   int n;
 };
 template <class T>
@@ -417,7 +418,7 @@ __global__ void __launch_bounds__(256) k_linear_rows_multi(const T* __restrict__
   if (i >= sg.n) return;
   const int o = blk * 8 + (threadIdx.x >> 5);
   if (o >= sg.O[i]) return;
-  linear_row<T>(sg.X[i] ? (const T*)sg.X[i] : X, (const T*)sg.W[i], (const T*)nullptr, sg.Y[i], sg.out32[i] != 0, N, sg.O[i], K, 0, o);
+  linear_row<T>(sg.X[i] ? (const T*)sg.X[i] : X, (const T*)sg.W[i], (const T*)nullptr, sg.Y[i], sg.out32[i] != 0, N, sg.O[i], K, sg.act[i], o);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

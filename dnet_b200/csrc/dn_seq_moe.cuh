@@ -167,12 +167,31 @@ __global__ void __launch_bounds__(256) k_moe_tiles(const T* __restrict__ X, cons
   }
 }
 
-// a few tokens: pair p = blockIdx.y is row p; one warp per output feature of the pair's expert
+// a few tokens: pair p = blockIdx.y is row p; one warp per output feature of the pair's expert.  Rows from P on (if the
+// grid has them) are the shared expert's: row P + n is token n on the shared matrices, with its own width and limit.
+struct SharedExpert {
+  const void *gate, *up, *down;
+  int ff;
+  float limit;
+  void* act;       // [N, ff]
+  float* out;      // [N, W]
+};
 template <class T, bool UP>
 __global__ void __launch_bounds__(256) k_moe_rows(const T* __restrict__ X, const void* const* __restrict__ etab, int E, const int32_t* __restrict__ idx,
-                                                  int top, void* __restrict__ Y, int O, int K, float limit) {
-  const int p = blockIdx.y, e = idx[p];
+                                                  int top, void* __restrict__ Y, int O, int K, float limit, int P, const T* __restrict__ h,
+                                                  SharedExpert sh) {
+  const int p = blockIdx.y;
   const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p >= P) {
+    const int n = p - P;
+    if (UP) {
+      if (o < sh.ff) linear_row<T>(h + (size_t)n * K, (const T*)sh.gate, (const T*)sh.up, (T*)sh.act + (size_t)n * sh.ff, false, 1, sh.ff, K, ACT_CGLU, o, sh.limit);
+    } else {
+      if (o < O) linear_row<T>((const T*)sh.act + (size_t)n * sh.ff, (const T*)sh.down, (const T*)nullptr, sh.out + (size_t)n * O, true, 1, O, sh.ff, ACT_NONE, o, 0.f);
+    }
+    return;
+  }
+  const int e = idx[p];
   if (o >= O) return;
   if (UP)
     linear_row<T>(X + (size_t)(p / top) * K, (const T*)etab[e], (const T*)etab[E + e], (T*)Y + (size_t)p * O, false, 1, O, K, ACT_CGLU, o, limit);

@@ -42,11 +42,19 @@ __global__ void k_shift_carry(const T* __restrict__ h, Batch b, int W, T* __rest
 // z [N, C] (in place), C = H dk:
 //   RECUR_AFTER: d = sigmoid(z + bias)^(1/tau) = exp(-softplus(-(z + bias)) / tau)
 //   RECUR_BONUS: d = exp(-exp(z + bias))
+// carry (optional, small steps): the block of an entry's last token also copies the token's mixer input row h[n] to
+// the slot's carried row (what k_shift_carry does for large steps; every reader of the old row ran before this kernel)
+template <class T>
+struct ShiftCarry { const T* h; T* state; size_t slot_stride; int W; const int32_t* first; const int32_t* slot; };
 template <class T>
 __global__ void k_decay_prep(int mode, int N, int C, int Cv, const T* __restrict__ Uq, const T* __restrict__ Uk, const T* __restrict__ Uv,
                              const T* __restrict__ bias, float qscale, float tau, float* __restrict__ qn, float* __restrict__ kn,
-                             float* __restrict__ vv, float* __restrict__ z) {
+                             float* __restrict__ vv, float* __restrict__ z, ShiftCarry<T> carry) {
   const int n = blockIdx.x;
+  if (carry.h && (n == N - 1 || carry.first[n + 1] != carry.first[n])) {
+    T* dst = carry.state + (size_t)carry.slot[n] * carry.slot_stride;
+    for (int c = threadIdx.x; c < carry.W; c += blockDim.x) dst[c] = carry.h[(size_t)n * carry.W + c];
+  }
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     const size_t i = (size_t)n * C + c;
     qn[i] = ldf(Uq + i) * qscale;
