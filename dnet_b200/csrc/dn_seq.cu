@@ -657,7 +657,7 @@ static cudaError_t gemm_tc_grouped(const CUtensorMap& x, const dn::TcParams& p, 
 // the expert products of a routed feed-forward: h [N, W] -> m->y [N, W] (routed sum), m->y2 (shared expert, if any);
 // fused: the sum of both goes through the norm after the sublayer into the plain residual in the combining kernel
 template <class T>
-static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, cudaStream_t s) {
+static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, NextNorm<T> nx, cudaStream_t s) {
   const dn_seq_layer_cfg& lc = l.c;
   const int W = m->cfg.width, E = lc.experts, top = lc.top, P = N * top;
   auto w = [&](int i) { return (const T*)l.w[i]; };
@@ -713,7 +713,7 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, cudaStream_t 
   }
   CK(mark(m, DN_SEQ_PH_WRITE_BACK, s));
   CK(launch(k_moe_combine<T>, dim3((unsigned)(((size_t)N * W + 255) / 256)), dim3(256), 0, s, (const float*)m->eo, (const float*)m->rwt, (const int32_t*)m->rpos, N, W, top,
-            m->y, fused ? m->xs : (float*)nullptr, lc.shared_ff > 0 ? (const float*)m->y2 : (const float*)nullptr, w(DN_SQ_POST2), w(DN_SQ_POST2_B), w(DN_SQ_POST2_ALPHA)));
+            m->y, fused ? m->xs : (float*)nullptr, lc.shared_ff > 0 ? (const float*)m->y2 : (const float*)nullptr, w(DN_SQ_POST2), w(DN_SQ_POST2_B), w(DN_SQ_POST2_ALPHA), nx));
   return DN_OK;
 }
 
@@ -756,10 +756,18 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     return launch(k_write_back<T, 1>, dim3(ew), dim3(256), 0, s, m->xs, N, W, S, mix, out, (const float*)m->y);
   };
   // a sublayer's output a y (+ b y2) joins the residual, through the norm after the sublayer where the model has one
-  auto join = [&](SeqLayer& l, int post, int hc_mix, int hc_out, float a, const float* y2, float bb) -> cudaError_t {
+  const NextNorm<T> no_next{nullptr, nullptr, nullptr, nullptr};
+  // the norm before the sublayer that follows, when the joining kernel can produce it (plain residual, both norms dynamic tanh)
+  const bool can_fuse_next = c.post_norm && dyt && S <= 0;
+  bool h_ready = false;
+  auto next_norm = [&](const SeqLayer& nl, int which) {
+    return NextNorm<T>{(const T*)nl.w[which], (const T*)nl.w[which == DN_SQ_NORM1 ? DN_SQ_NORM1_B : DN_SQ_NORM2_B],
+                       (const T*)nl.w[which == DN_SQ_NORM1 ? DN_SQ_NORM1_ALPHA : DN_SQ_NORM2_ALPHA], (T*)m->h};
+  };
+  auto join = [&](SeqLayer& l, int post, int hc_mix, int hc_out, float a, const float* y2, float bb, NextNorm<T> nx) -> cudaError_t {
     auto w = [&](int i) { return (const T*)l.w[i]; };
     if (c.post_norm) {
-      if (S <= 0) return launch(k_dyt_add<T>, dim3(ew), dim3(256), 0, s, m->xs, NW, W, (const float*)m->y, a, y2, bb, w(post), w(post + 1), w(post + 2));
+      if (S <= 0) return launch(k_dyt_add<T>, dim3(ew), dim3(256), 0, s, m->xs, NW, W, (const float*)m->y, a, y2, bb, w(post), w(post + 1), w(post + 2), nx);
       cudaError_t e = launch(k_dyt_inplace<T>, dim3(ew), dim3(256), 0, s, m->y, NW, W, a, y2, bb, w(post), w(post + 1), w(post + 2));
       if (e != cudaSuccess) return e;
     } else if (y2 || a != 1.f) {
@@ -786,8 +794,13 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     }
     // ---- mixer sublayer
     PH(DN_SEQ_PH_NORM);
-    CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
-              w(DN_SQ_NORM1_B), dyt ? w(DN_SQ_NORM1_ALPHA) : (const T*)nullptr));
+    if (!h_ready || run.inject)
+      CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
+                w(DN_SQ_NORM1_B), dyt ? w(DN_SQ_NORM1_ALPHA) : (const T*)nullptr));
+    h_ready = false;
+    // what the join after this run's last sublayer can prepare: the next run's first norm, unless a loop pass starts there
+    const bool next_ok = can_fuse_next && ri + 1 < (int)m->runs.size() && !m->runs[ri + 1].inject;
+    const NextNorm<T> nx_run = next_ok ? next_norm(m->L[m->runs[ri + 1].layer], DN_SQ_NORM1) : no_next;
     T* cst = (T*)m->conv_state + run.conv_off;
     float* st = m->delta_state + run.state_off;
     const bool few = N <= 8;      // a decode step: all projections of the mixer in one launch of the row kernel
@@ -930,24 +943,29 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       ja = lc.left_scale; jb = lc.right_scale; jy2 = m->y2;
     }
     PH(DN_SEQ_PH_WRITE_BACK);
-    CK(join(l, DN_SQ_POST1, DN_SQ_HC1_MIX, DN_SQ_HC1_OUT, ja, jy2, jb));
+    const NextNorm<T> nx_mix = lc.ff > 0 ? (can_fuse_next ? next_norm(l, DN_SQ_NORM2) : no_next) : nx_run;
+    CK(join(l, DN_SQ_POST1, DN_SQ_HC1_MIX, DN_SQ_HC1_OUT, ja, jy2, jb, nx_mix));
+    if (lc.ff == 0) h_ready = nx_run.alpha != nullptr;
     // ---- feed-forward sublayer
     if (lc.ff > 0) {
       PH(DN_SEQ_PH_NORM);
-      CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
-                w(DN_SQ_NORM2_B), dyt ? w(DN_SQ_NORM2_ALPHA) : (const T*)nullptr));
+      if (!can_fuse_next)
+        CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
+                  w(DN_SQ_NORM2_B), dyt ? w(DN_SQ_NORM2_ALPHA) : (const T*)nullptr));
       if (lc.mlp_kind == DN_MLP_MOE) {
         const bool fused = c.post_norm && S <= 0;
-        const int rc = moe_ff<T>(m, l, N, fused, s);
+        const int rc = moe_ff<T>(m, l, N, fused, fused ? nx_run : no_next, s);
         if (rc != DN_OK) return rc;
-        if (!fused) CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, lc.shared_ff > 0 ? (const float*)m->y2 : nullptr, 1.f));
+        if (!fused) CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, lc.shared_ff > 0 ? (const float*)m->y2 : nullptr, 1.f, nx_run));
+        h_ready = nx_run.alpha != nullptr;
       } else {
         PH(DN_SEQ_PH_FF_UP);
         CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, ACT_GEGLU, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));
         PH(DN_SEQ_PH_FF_DOWN);
         CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0, LinMaps{wm(DN_SQ_DOWN), nullptr, &l.x_act}));
         PH(DN_SEQ_PH_WRITE_BACK);
-        CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, nullptr, 0.f));
+        CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, nullptr, 0.f, nx_run));
+        h_ready = nx_run.alpha != nullptr && c.post_norm && S <= 0;
       }
     }
     PH(DN_SEQ_PH_OTHER);

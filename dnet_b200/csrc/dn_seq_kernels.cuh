@@ -218,15 +218,20 @@ __global__ void k_write_back(float* __restrict__ xs, int N, int W, int S, const 
 
 // a sublayer's output normed again (dynamic tanh) before it joins the plain residual:
 //   x <- x + dyt(a y + b y2)        (y2 optional: two branches of a mixer, or routed + shared experts)
+// and, since the norm before the next sublayer is elementwise too, its output in the same pass: h <- dyt'(x)
+template <class T>
+struct NextNorm { const T *w, *b, *alpha; T* h; };      // alpha == null: none
 template <class T>
 __global__ void k_dyt_add(float* __restrict__ x, size_t NW, int W, const float* __restrict__ y, float a, const float* __restrict__ y2, float b,
-                          const T* __restrict__ nw, const T* __restrict__ nb, const T* __restrict__ nalpha) {
+                          const T* __restrict__ nw, const T* __restrict__ nb, const T* __restrict__ nalpha, NextNorm<T> nx) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= NW) return;
   const int c = (int)(i % W);
   float v = a * y[i];
   if (y2) v += b * y2[i];
-  x[i] += dyt_f(v, ldf(nalpha), nw, nb, c);
+  const float xn = x[i] + dyt_f(v, ldf(nalpha), nw, nb, c);
+  x[i] = xn;
+  if (nx.alpha) stf(nx.h + i, dyt_f(xn, ldf(nx.alpha), nx.w, nx.b, c));
 }
 // the same, in place, for models with residual streams (the write-back follows): y <- dyt(a y + b y2)
 template <class T>

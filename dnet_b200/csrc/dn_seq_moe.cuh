@@ -218,15 +218,18 @@ __global__ void k_moe_gather(const T* __restrict__ h, const int32_t* __restrict_
 template <class T>
 __global__ void k_moe_combine(const float* __restrict__ eo, const float* __restrict__ wt, const int32_t* __restrict__ pos, int N, int W, int top,
                               float* __restrict__ y, float* __restrict__ x, const float* __restrict__ y2, const T* __restrict__ nw,
-                              const T* __restrict__ nb, const T* __restrict__ nalpha) {
+                              const T* __restrict__ nb, const T* __restrict__ nalpha, NextNorm<T> nx) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)N * W) return;
   const size_t n = i / W;
   const int c = (int)(i % W);
   float a = 0.f;
   for (int j = 0; j < top; j++) a = fmaf(wt[n * top + j], eo[(size_t)pos[n * top + j] * W + c], a);
-  if (x) x[i] += dyt_f(a + (y2 ? y2[i] : 0.f), ldf(nalpha), nw, nb, c);
-  else y[i] = a;
+  if (x) {
+    const float xn = x[i] + dyt_f(a + (y2 ? y2[i] : 0.f), ldf(nalpha), nw, nb, c);
+    x[i] = xn;
+    if (nx.alpha) stf(nx.h + i, dyt_f(xn, ldf(nx.alpha), nx.w, nx.b, c));      // the norm before the next sublayer, while x is at hand
+  } else y[i] = a;
 }
 
 }  // namespace dnseq
