@@ -731,8 +731,9 @@ static int decay_rule(dn_seq_model* m, const Batch& b, int mode, int H, int dk, 
   const int cols = P >= 2 ? 16 : 32;
   dim3 grid(b.E * H, (dv + cols - 1) / cols);
   const int per = 3 * P * (R + 4) + cols;
-  int TB = std::max(1, std::min(16, 4500 / per));
-  if (TB >= 4) TB &= ~3;      // whole groups of the kernel's four-token batches
+  int TB = std::max(1, std::min(16, 5800 / per));      // two tiles within ~46 KB of shared memory
+  if (TB >= 8) TB &= ~7;      // whole groups of the kernel's token batches
+  else if (TB >= 4) TB = 4;
   const size_t dsm = (size_t)2 * TB * per * 4;
 #define DR(Rv, Pv, Cv_) if (R == Rv && P == Pv) CK(launch(k_decay_rule<Rv, Pv, Cv_>, grid, dim3(Cv_ * Pv), dsm, s, mode, b, H, dk, dv, TB, (const float*)m->qn, \
                          (const float*)m->kn, (const float*)m->vv, (const float*)m->dz, bonus, m->esz == 4 ? 1 : 0, st, m->delta_stride, m->od))

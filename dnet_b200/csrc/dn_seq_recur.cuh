@@ -71,9 +71,9 @@ __global__ void k_decay_prep(int mode, int N, int C, int Cv, const T* __restrict
 // come through shared memory in tiles of TB tokens, copied asynchronously one tile ahead; k, q and the decay lie
 // there as P runs of R values, each run padded by 4 floats (the 16-byte reads of a column's P lanes fall into
 // different banks); rows from dk up are zero.  The read-out sums a thread's rows in ascending order, then the lanes
-// of a column pairwise: an order fixed by (dk, P), whatever the tile size or the cut of a prompt.  Four tokens are
-// taken at a time: their state updates run back to back and their read-outs are reduced together (four independent
-// shuffle chains in flight).
+// of a column pairwise: an order fixed by (dk, P), whatever the tile size or the cut of a prompt.  U tokens (8 in
+// blocks of up to 128 threads, else 4) are taken at a time: their loads are issued ahead, their state updates run back
+// to back and their read-outs are reduced together (U independent shuffle chains in flight).
 template <int R, int P, int COLS>
 __global__ void __launch_bounds__(COLS * P) k_decay_rule(int mode, Batch b, int H, int dk, int dv, int TB, const float* __restrict__ qn,
                                                          const float* __restrict__ kn, const float* __restrict__ vv,
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(COLS * P) k_decay_rule(int mode, Batch b, int 
   extern __shared__ __align__(16) float dsm[];      // 2 x TB x per
   constexpr int KP = P * (R + 4);
   constexpr int per = 3 * KP + COLS;                // k q decay v[COLS]
-  constexpr int U = 4;
+  constexpr int U = COLS * P <= 128 ? 8 : 4;      // tokens a group: as many as the registers of the block size allow
   const int e = blockIdx.x / H, h = blockIdx.x % H;
   const int part = threadIdx.x % P, colb = threadIdx.x / P, col = blockIdx.y * COLS + colb;
   const int s0 = b.ent_start[e], s1 = b.ent_start[e + 1];
@@ -129,32 +129,40 @@ __global__ void __launch_bounds__(COLS * P) k_decay_rule(int mode, Batch b, int 
     const int cnt = min(TB, s1 - n0);
     for (int t0 = 0; t0 < cnt; t0 += U) {
       float od[U];
+      auto token = [&](int uu) {
+        const float* in = dsm + ((size_t)buf * TB + t0 + uu) * per;
+        const float4* k4 = reinterpret_cast<const float4*>(in + part * (R + 4));
+        const float4* q4 = reinterpret_cast<const float4*>(in + KP + part * (R + 4));
+        const float4* d4 = reinterpret_cast<const float4*>(in + 2 * KP + part * (R + 4));
+        const float v = in[3 * KP + colb];
+        float acc = 0.f;
 #pragma unroll
-      for (int uu = 0; uu < U; uu++) {
-        od[uu] = 0.f;
-        if (t0 + uu < cnt) {
-          const float* in = dsm + ((size_t)buf * TB + t0 + uu) * per;
-          const float4* k4 = reinterpret_cast<const float4*>(in + part * (R + 4));
-          const float4* q4 = reinterpret_cast<const float4*>(in + KP + part * (R + 4));
-          const float4* d4 = reinterpret_cast<const float4*>(in + 2 * KP + part * (R + 4));
-          const float v = in[3 * KP + colb];
+        for (int j = 0; j < R / 4; j++) {
+          const float4 kv = k4[j], qv = q4[j], dv4 = d4[j];
+          const float kk[4] = {kv.x, kv.y, kv.z, kv.w}, qq[4] = {qv.x, qv.y, qv.z, qv.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
 #pragma unroll
-          for (int j = 0; j < R / 4; j++) {
-            const float4 kv = k4[j], qv = q4[j], dv4 = d4[j];
-            const float kk[4] = {kv.x, kv.y, kv.z, kv.w}, qq[4] = {qv.x, qv.y, qv.z, qv.w}, dd[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-              const float kvp = kk[i] * v;
-              float& Sr = S[4 * j + i];
-              if (mode == RECUR_BONUS) {
-                od[uu] = fmaf(fmaf(u[4 * j + i], kvp, Sr), qq[i], od[uu]);
-                Sr = fmaf(dd[i], Sr, kvp);
-              } else {
-                Sr = fmaf(dd[i], Sr, kvp);
-                od[uu] = fmaf(Sr, qq[i], od[uu]);
-              }
+          for (int i = 0; i < 4; i++) {
+            const float kvp = kk[i] * v;
+            float& Sr = S[4 * j + i];
+            if (mode == RECUR_BONUS) {
+              acc = fmaf(fmaf(u[4 * j + i], kvp, Sr), qq[i], acc);
+              Sr = fmaf(dd[i], Sr, kvp);
+            } else {
+              Sr = fmaf(dd[i], Sr, kvp);
+              acc = fmaf(Sr, qq[i], acc);
             }
           }
+        }
+        od[uu] = acc;
+      };
+      if (t0 + U <= cnt) {      // a whole group: no guards, so that the four tokens' loads can be issued ahead of the arithmetic
+#pragma unroll
+        for (int uu = 0; uu < U; uu++) token(uu);
+      } else {
+#pragma unroll
+        for (int uu = 0; uu < U; uu++) {
+          od[uu] = 0.f;
+          if (t0 + uu < cnt) token(uu);
         }
       }
 #pragma unroll
