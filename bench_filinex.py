@@ -23,9 +23,9 @@ def filinex_config(sz: dict) -> dict:
            "shared": {"ff": ff // 2, "limit": 7.0}}
     wkv = {"type": "wkv", "mixer": {"heads": W // 64, "dim": 64, "rank": RANK}, "mlp": moe}
     par = {"type": "parallel", "mlp": moe,
-           "mixer": {"left": {"heads": H, "kv_heads": G, "dim": HD, "vdim": HD, "scale": HD ** -0.5, "softcap": 50.0},
-                     "right": {"heads": H // 2, "dim": 64, "vdim": HD, "tau": 16.0, "rank": RANK}, "left_scale": 1.0, "right_scale": 0.5}}
-    return {"architecture": "Filinex", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+           "mixer": {"left": {"heads": H, "kv_heads": G, "dim": HD, "vdim": HD, "scale": HD ** -0.5, "softcap": 30.0},
+                     "right": {"heads": H // 2, "dim": 64, "vdim": HD, "tau": 8.0, "rank": RANK}, "left_scale": 1.0, "right_scale": 0.5}}
+    return {"architecture": "Filinex", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-5}, "logit_softcap": 20.0,
             "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [wkv, par, wkv, par]}
 
 
@@ -105,10 +105,12 @@ def filinex_algorithmic(cfg: dict, N: int, ctx0: int, n_seqs: int) -> dict:
             by["moe_down"] += 2.0 * hit * W * ef
             if mlp.get("shared"):
                 sf = mlp["shared"]["ff"]
-                f["ff_up"] += 4.0 * N * W * sf
-                by["ff_up"] += 4.0 * W * sf
-                f["ff_down"] += 2.0 * N * W * sf
-                by["ff_down"] += 2.0 * W * sf
+                # steps of up to 8 tokens run the shared expert's rows inside the routed experts' two launches
+                up, down = ("moe_up", "moe_down") if N <= 8 else ("ff_up", "ff_down")
+                f[up] += 4.0 * N * W * sf
+                by[up] += 4.0 * W * sf
+                f[down] += 2.0 * N * W * sf
+                by[down] += 2.0 * W * sf
     return {"flops": f, "bytes": by}
 
 
