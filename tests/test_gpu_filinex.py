@@ -407,7 +407,7 @@ def test_greedy_generation_through_the_batcher():
 
 
 def test_command_lines_on_a_checkpoint_folder(tmp_path):
-    """bin/trace_run on a folder with config.json and model.safetensors: the class is picked by the
+    """bin/trace_run and bin/generate on a folder with config.json and model.safetensors: the class is picked by the
     config's architecture, the sizes the config lacks come from the tensors' shapes"""
     import json
     import os
@@ -445,6 +445,21 @@ def test_command_lines_on_a_checkpoint_folder(tmp_path):
     assert err(got[0], ref[[49]]) < TOL["float32"]
     assert err(got[1], torch.cat([ref[[50, 51]], fo.forward(cfg, w, t[:9])[[8]]])) < TOL["float32"]
     assert err(got[2], ref[[69]]) < TOL["float32"]
+    # bin/generate: greedy continuation of two prompts through the batcher's token loop, in fp32
+    reqs = [{"id": "x", "prompt": t[:40], "max_new_tokens": 5}, {"id": "y", "prompt": t[:7], "max_new_tokens": 3}]
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "generate"), "--model", str(folder), "--dtype", "float32", "--max-tokens", "192",
+                        "--step-tokens", "16"], input="\n".join(json.dumps(r) for r in reqs) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    outs = {o["id"]: o["tokens"] for o in map(json.loads, p.stdout.strip().splitlines())}
+    for r in reqs:
+        seq = list(r["prompt"])
+        assert len(outs[r["id"]]) == r["max_new_tokens"]
+        for tok in outs[r["id"]]:
+            lg = fo.forward(cfg, w, seq)[-1]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) > 1e-3:
+                assert tok == int(lg.argmax())
+            seq.append(tok)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
