@@ -84,6 +84,12 @@ __device__ __forceinline__ float act_apply(int act, float a, float b, float lim)
   if (act == ACT_CGLU) return clamped_glu_f(a, b, lim);
   return a;
 }
+// sum += v with the rounding error of the addition carried in c (compensated summation)
+__device__ __forceinline__ void kahan_add(float& sum, float& c, float v) {
+  const float y = __fsub_rn(v, c), t = __fadd_rn(sum, y);
+  c = __fsub_rn(__fsub_rn(t, sum), y);
+  sum = t;
+}
 // dynamic tanh: tanh(alpha x) w + b
 template <class T>
 __device__ __forceinline__ float dyt_f(float x, float alpha, const T* __restrict__ w, const T* __restrict__ b, int c) {
@@ -273,7 +279,10 @@ __global__ void k_stream_sum(const float* __restrict__ xs, int N, int W, int S1,
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Y[N, O] = X[N, K] W[O, K]^T, fp32 accumulation in ascending k; CUDA-core tiles (any N, O, K).
+// Y[N, O] = X[N, K] W[O, K]^T on CUDA-core tiles (any N, O, K).  fp32 accumulation: the 16 products of a k-block are
+// summed from zero in ascending k, and the blocks' sums are added with a compensation term (Kahan), so the rounding
+// error of a long reduction stays that of one block -- the fp32 mode's products then match the few-row kernel's
+// (lane partials + tree) to the last bits, whatever the step's size.
 // OUT32: write fp32 (residual-side outputs), else T.  act: ACT_* (the two-operand ones read W2 as well).
 template <class T, bool OUT32>
 __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
@@ -283,11 +292,11 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
   __shared__ float Xs[BK][BM + 4], Ws[BK][BN + 4], Vs[BK][BN + 4];
   const int n0 = blockIdx.y * BM, o0 = blockIdx.x * BN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  float acc[4][4], acc2[4][4];
+  float acc[4][4], acc2[4][4], cmp[4][4], cmp2[4][4];
 #pragma unroll
   for (int i = 0; i < 4; i++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) acc[i][j] = acc2[i][j] = 0.f;
+    for (int j = 0; j < 4; j++) acc[i][j] = acc2[i][j] = cmp[i][j] = cmp2[i][j] = 0.f;
   for (int k0 = 0; k0 < K; k0 += BK) {
     for (int e = threadIdx.x; e < BM * BK; e += 256) {
       const int r = e / BK, c = e % BK;
@@ -296,6 +305,11 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
       if (two) Vs[c][r] = (o0 + r < O && k0 + c < K) ? ldf(W2 + (size_t)(o0 + r) * K + k0 + c) : 0.f;
     }
     __syncthreads();
+    float part[4][4], part2[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) part[i][j] = part2[i][j] = 0.f;
 #pragma unroll
     for (int k = 0; k < BK; k++) {
       float a[4], w[4];
@@ -306,16 +320,23 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
 #pragma unroll
       for (int i = 0; i < 4; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        for (int j = 0; j < 4; j++) part[i][j] = fmaf(a[i], w[j], part[i][j]);
       if (two) {
 #pragma unroll
         for (int j = 0; j < 4; j++) w[j] = Vs[k][tx * 4 + j];
 #pragma unroll
         for (int i = 0; i < 4; i++)
 #pragma unroll
-          for (int j = 0; j < 4; j++) acc2[i][j] = fmaf(a[i], w[j], acc2[i][j]);
+          for (int j = 0; j < 4; j++) part2[i][j] = fmaf(a[i], w[j], part2[i][j]);
       }
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        kahan_add(acc[i][j], cmp[i][j], part[i][j]);
+        if (two) kahan_add(acc2[i][j], cmp2[i][j], part2[i][j]);
+      }
     __syncthreads();
   }
 #pragma unroll

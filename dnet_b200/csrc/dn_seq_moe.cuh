@@ -118,11 +118,11 @@ __global__ void __launch_bounds__(256) k_moe_tiles(const T* __restrict__ X, cons
   __syncthreads();
   const int o0 = blockIdx.x * BN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  float acc[4][4], acc2[4][4];
+  float acc[4][4], acc2[4][4], cmp[4][4], cmp2[4][4];      // block sums added with compensation, as in k_linear
 #pragma unroll
   for (int i = 0; i < 4; i++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) acc[i][j] = acc2[i][j] = 0.f;
+    for (int j = 0; j < 4; j++) acc[i][j] = acc2[i][j] = cmp[i][j] = cmp2[i][j] = 0.f;
   for (int k0 = 0; k0 < K; k0 += BK) {
     for (int el = threadIdx.x; el < BM * BK; el += 256) {
       const int r = el / BK, c = el % BK;
@@ -131,6 +131,11 @@ __global__ void __launch_bounds__(256) k_moe_tiles(const T* __restrict__ X, cons
       if (UP) Vs[c][r] = (o0 + r < O && k0 + c < K) ? ldf(Wb + (size_t)(o0 + r) * K + k0 + c) : 0.f;
     }
     __syncthreads();
+    float part[4][4], part2[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) part[i][j] = part2[i][j] = 0.f;
 #pragma unroll
     for (int k = 0; k < BK; k++) {
       float a[4], w[4];
@@ -141,16 +146,23 @@ __global__ void __launch_bounds__(256) k_moe_tiles(const T* __restrict__ X, cons
 #pragma unroll
       for (int i = 0; i < 4; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        for (int j = 0; j < 4; j++) part[i][j] = fmaf(a[i], w[j], part[i][j]);
       if (UP) {
 #pragma unroll
         for (int j = 0; j < 4; j++) w[j] = Vs[k][tx * 4 + j];
 #pragma unroll
         for (int i = 0; i < 4; i++)
 #pragma unroll
-          for (int j = 0; j < 4; j++) acc2[i][j] = fmaf(a[i], w[j], acc2[i][j]);
+          for (int j = 0; j < 4; j++) part2[i][j] = fmaf(a[i], w[j], part2[i][j]);
       }
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        kahan_add(acc[i][j], cmp[i][j], part[i][j]);
+        if (UP) kahan_add(acc2[i][j], cmp2[i][j], part2[i][j]);
+      }
     __syncthreads();
   }
 #pragma unroll
